@@ -104,7 +104,7 @@ __device__ __forceinline__ double warp_sum_d(double v) {
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return (uint32_t) __cvta_generic_to_shared(p); }
 
-// ---- mbarrier + bulk async copy (TMA 1-D, SASS UBLKCP) ----
+// ---- mbarrier + bulk async copy (TMA 1-D) ----
 __device__ __forceinline__ void mbar_init(uint64_t * bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }

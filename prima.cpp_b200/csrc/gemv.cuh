@@ -12,7 +12,7 @@
 //     rest of A drains; a small kernel between two GEMVs (attention, silu-quant) runs while the next GEMV's rings fill.
 //     Round 1's single 512-thread / 227-KB CTA per SM serialised every launch boundary: 9.25 us fixed cost per launch
 //     (profiles/r1_gemv_microbench.txt) x 321 launches = 3 ms of a 10-ms token;
-//   * row tiles of raw blocks stream HBM -> shared memory with cp.async.bulk (1-D TMA, SASS UBLKCP) into an nstage-deep ring
+//   * row tiles of raw blocks stream HBM -> shared memory with cp.async.bulk (1-D TMA) into an nstage-deep ring
 //     (4-8 stages of ~16-24 KB chosen per launch; ~185 KB in flight per SM).  There is no producer warp: the consumer warp
 //     that finishes a stage last re-arms its mbarrier and issues the refill itself;
 //   * 8 consumer warps; ONE LANE OWNS ONE SUPER-BLOCK COLUMN: lane l of sub-warp s keeps the 256 int8 activations of
