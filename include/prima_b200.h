@@ -38,7 +38,8 @@ extern "C" {
 #define PB200_API __attribute__((visibility("default")))
 
 /* enum ggml_type values used on this path (ggml/include/ggml.h:356-395) */
-enum { PB200_TYPE_F32 = 0, PB200_TYPE_F16 = 1, PB200_TYPE_Q5_1 = 7, PB200_TYPE_Q8_0 = 8, PB200_TYPE_Q4_K = 12, PB200_TYPE_Q5_K = 13, PB200_TYPE_Q6_K = 14 };
+enum { PB200_TYPE_F32 = 0, PB200_TYPE_F16 = 1, PB200_TYPE_Q5_1 = 7, PB200_TYPE_Q8_0 = 8, PB200_TYPE_Q4_K = 12, PB200_TYPE_Q5_K = 13, PB200_TYPE_Q6_K = 14,
+       PB200_TYPE_BF16 = 30 /* dense weights of the layer-list family */ };
 
 enum { PB200_EINVAL = -1, PB200_ENOMEM = -2, PB200_ENOTSUP = -3, PB200_ESTATE = -4, PB200_EABORTED = -5 };
 
@@ -235,6 +236,52 @@ PB200_API int pb200_profile_step(pb200_model * m, int32_t token, int32_t pos, do
 PB200_API int pb200_set_hidden(pb200_model * m, const float * hidden_host);   /* host -> hidden_in (tests, host-staged hand-off) */
 PB200_API int pb200_debug_read(pb200_model * m, const char * name, float * host, int64_t n);   /* white-box tests: q,k,v,att,g,u,x_a,x_b,xn,logits */
 PB200_API int pb200_set_use_graph(pb200_model * m, int on);             /* CUDA-graph replay on/off (default on) */
+
+/* ---- architectures ----
+ * Two families share the model object: 0 = one fixed transformer graph over k-quant GGUF weights ("llama", "qwen2":
+ * pb200_model_create / pb200_model_load_gguf), 1 = layer list: a configuration file lists the layers, each with a sequence mixer
+ * (windowed attention with kept first tokens, or a Mamba-2 state-space mixer) and an optional gated feed-forward, over dense f32 / bf16
+ * weights ("Vamidra": pb200_model_create_from_config / pb200_model_load_dir).  pb200_arch_family: -1 for an unknown name. */
+PB200_API int          pb200_arch_count(void);
+PB200_API const char * pb200_arch_name(int i);
+PB200_API int          pb200_arch_family(const char * name);
+
+/* ---- layer-list family ----
+ * config_json: the text of the model's configuration file; its "architecture" selects the design.  compute_type: PB200_TYPE_BF16 (dense
+ * products on bf16 operands with fp32 accumulation; norms, attention scores and weights, the residual stream and all recurrent state stay
+ * fp32) or PB200_TYPE_F32 (everything in true fp32).  n_ctx: the most positions one sequence can have where a layer has to keep all of
+ * them; a windowed attention layer keeps keep_first + window rows per sequence whatever its length.  n_seq: sequence slots
+ * (<= 0: as many as 8 GiB of state hold, 4 .. 64).  Tensors arrive through pb200_model_set_tensor under their checkpoint names with
+ * type PB200_TYPE_BF16 or PB200_TYPE_F32 (converted to what the model computes in); then pb200_model_finalize.  pb200_model_synth
+ * fills every tensor with random values instead (benchmarks). */
+PB200_API pb200_model * pb200_model_create_from_config(const char * config_json, int compute_type, int device, int n_ctx, int n_seq);
+/* <dir>/config.json + <dir>/model.safetensors -> finalized model */
+PB200_API int pb200_model_load_dir(const char * dir, int compute_type, int device, int n_ctx, int n_seq, pb200_model ** out);
+PB200_API int pb200_model_get_hparams(const pb200_model * m, pb200_hparams * out);   /* n_layer, n_embd, n_vocab, n_ctx are set for every family */
+PB200_API int pb200_model_n_seq(const pb200_model * m);
+
+/* Sequence slots.  A slot holds everything a sequence carries from token to token (attention rows, convolution inputs, recurrent
+ * state); pb200_seq_alloc hands out a free slot in the empty state (>= 0, or PB200_ENOMEM), pb200_seq_free gives it back. */
+PB200_API int pb200_seq_alloc(pb200_model * m);
+PB200_API int pb200_seq_free(pb200_model * m, int slot);
+PB200_API int pb200_seq_length(pb200_model * m, int slot);   /* tokens the slot has seen; < 0: free slot */
+
+/* One step of a ragged batch: entry e appends n_tokens tokens to sequence slot seq (continuing at the slot's length) and asks for the
+ * logits at the token indices want[0..n_want) of its tokens.  logits_host receives the wanted rows, [sum n_want][n_vocab] f32, in the
+ * order of the entries and of want; greedy_host (optional) receives per entry the arg-max token of the logits after its last token.
+ * Entries that start a sequence run together as one prompt batch; entries that continue one advance token by token, all of them
+ * batched per token.  The logits of a position do not depend on what else is in the batch beyond fp32 rounding. */
+typedef struct pb200_batch_entry {
+    int32_t seq;
+    int32_t n_tokens;
+    const int32_t * tokens;
+    int32_t n_want;
+    const int32_t * want;
+} pb200_batch_entry;
+PB200_API int pb200_batch_step(pb200_model * m, int n_entries, const pb200_batch_entry * entries, float * logits_host, int32_t * greedy_host);
+/* white-box tests: on != 0 keeps the residual stream after every layer run of the next batches; read it with
+ * pb200_debug_read(m, "layers", host, runs * tokens * n_embd) */
+PB200_API int pb200_debug_tap_layers(pb200_model * m, int on);
 
 #ifdef __cplusplus
 }

@@ -18,10 +18,19 @@
 
 #include "../../include/prima_b200.h"
 #include "launch.h"
+#include "model.h"
 
 using namespace pb;
 
 std::atomic<uint64_t> g_launches{0};
+
+// layer-list family (layers.cu): the model-object entry points below forward there when m->ll is set
+int ll_set_tensor(pb200_model * m, const char * name, int type, const void * host, size_t nbytes);
+int ll_synth(pb200_model * m, uint64_t seed);
+int ll_finalize(pb200_model * m);
+void ll_free(pb200_model * m);
+int ll_debug_read(pb200_model * m, const char * name, float * host, int64_t n);
+#define NOT_FOR_LAYER_LIST(m) do { if ((m) && (m)->ll) return PB200_ENOTSUP; } while (0)
 
 #define CK(expr)                                  \
     do {                                          \
@@ -44,25 +53,6 @@ static int dbg_sync(cudaStream_t st, const char * what) {
 
 namespace {
 
-struct Tensor {
-    void * data = nullptr;
-    int type = -1;
-    int64_t N = 0, K = 0;
-    size_t bytes = 0;
-};
-
-struct Layer {
-    float *attn_norm = nullptr, *ffn_norm = nullptr;
-    Tensor wq, wk, wv, wo, gate, up, down;
-    float *bq = nullptr, *bk = nullptr, *bv = nullptr;
-};
-
-struct ActBuf {
-    ActQ q{};
-    void * base = nullptr;
-    int64_t K = 0;
-};
-
 size_t act_ws_bytes(int64_t k) {
     const int64_t kp = (k + 255) / 256 * 256;
     // qs[kp] | d[kp/32] f32 | s[kp/32] f32 | bsums[kp/16] i16     (all 16-B aligned since kp % 256 == 0)
@@ -80,51 +70,6 @@ ActQ act_from_ws(void * ws, int64_t k) {
 }
 
 }  // namespace
-
-struct pb200_model {
-    pb200_hparams hp{};
-    int device = 0, l0 = 0, l1 = 0;
-    bool with_embd = false, with_head = false, finalized = false, use_graph = true;
-    cudaStream_t stream = nullptr;
-    Tensor tok_embd, output;
-    float *output_norm = nullptr, *rope_ff = nullptr;
-    std::vector<Layer> layers;   // index il - l0
-    __half *kcache = nullptr, *vcache = nullptr;
-    float *x_in = nullptr, *x_a = nullptr, *x_b = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *g = nullptr, *u = nullptr,
-          *xn = nullptr, *x_out = nullptr, *logits = nullptr;
-    ActBuf actE, actQD, actF;
-    unsigned int * gbar = nullptr;     // grid-barrier state of the distributed GEMV prologues (2 words, self-resetting)
-    int32_t * tokpos_dev = nullptr;    // [0] token, [1] pos
-    int32_t * tokpos_host = nullptr;   // pinned
-    float * logits_host = nullptr;     // pinned
-    RopeParams rp{};
-    int n_seq = 1;                      // independent sequences with their own KV cache / token / position (the pipeline keeps one per stage in flight)
-    std::vector<cudaGraphExec_t> graph_exec;   // one captured step per sequence slot
-    int32_t * sample_dev = nullptr;     // [n_seq] greedy token of the last step (pb200_argmax_seq)
-    uint64_t launches_per_step = 0;
-    int64_t weight_bytes = 0;
-    std::vector<void *> allocs;
-    bool profiling = false;
-    // prompt-processing (prefill) scratch, grown on demand
-    struct Prefill {
-        int T = 0;
-        float *x0 = nullptr, *x1 = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *g = nullptr, *u = nullptr;
-        void * ws = nullptr;
-        int32_t *tok = nullptr, *pos = nullptr;
-        std::vector<void *> allocs;
-    } pf;
-    std::vector<cudaEvent_t> prof_ev;
-    std::vector<int64_t> prof_bytes;
-    size_t prof_n = 0;
-
-    int alloc(void ** p, size_t bytes) {
-        bytes = (bytes + 255) / 256 * 256;
-        cudaError_t e = cudaMalloc(p, bytes);
-        if (e != cudaSuccess) return (int) e;
-        allocs.push_back(*p);
-        return 0;
-    }
-};
 
 // ---------------------------------------------------------------------------------------------------------------
 // synthetic raw blocks generated on the device (bench without a checkpoint): valid bit patterns, weight std ~ 1/sqrt(K)
@@ -242,6 +187,7 @@ void pb200_model_free(pb200_model * m) {
     if (!m) return;
     cudaSetDevice(m->device);
     cudaStreamSynchronize(m->stream);
+    ll_free(m);
     for (cudaGraphExec_t ge : m->graph_exec) if (ge) cudaGraphExecDestroy(ge);
     for (void * p : m->allocs) cudaFree(p);
     for (void * p : m->pf.allocs) cudaFree(p);
@@ -255,6 +201,7 @@ void pb200_model_free(pb200_model * m) {
 // The caller fills it (pb200_model_set_tensor: one synchronous copy; gguf.cu: pinned double-buffered stream from the file).
 int pb200_model_tensor_alloc(pb200_model * m, const char * name, int type, size_t nbytes, void ** dev_ptr) {
     if (!m || !name || !dev_ptr) return PB200_EINVAL;
+    NOT_FOR_LAYER_LIST(m);
     *dev_ptr = nullptr;
     if (m->finalized) return PB200_ESTATE;
     cudaSetDevice(m->device);
@@ -287,6 +234,7 @@ int pb200_model_tensor_alloc(pb200_model * m, const char * name, int type, size_
 
 int pb200_model_set_tensor(pb200_model * m, const char * name, int type, const void * host_data, size_t nbytes) {
     if (!host_data) return PB200_EINVAL;
+    if (m && m->ll) return name ? ll_set_tensor(m, name, type, host_data, nbytes) : PB200_EINVAL;
     void * dev = nullptr;
     const int rc = pb200_model_tensor_alloc(m, name, type, nbytes, &dev);
     if (rc || !dev) return rc;
@@ -295,6 +243,7 @@ int pb200_model_set_tensor(pb200_model * m, const char * name, int type, const v
 
 int pb200_model_synth(pb200_model * m, int ftype, uint64_t seed) {
     if (!m) return PB200_EINVAL;
+    if (m->ll) return ll_synth(m, seed);
     if (m->finalized) return PB200_ESTATE;
     cudaSetDevice(m->device);
     const pb200_hparams & hp = m->hp;
@@ -496,6 +445,7 @@ static int enqueue_step(pb200_model * m, int seq, uint64_t * nlaunch) {
 
 int pb200_model_finalize(pb200_model * m) {
     if (!m) return PB200_EINVAL;
+    if (m->ll) return ll_finalize(m);
     if (m->finalized) return 0;
     cudaSetDevice(m->device);
     const pb200_hparams & hp = m->hp;
@@ -583,6 +533,7 @@ int64_t pb200_model_weight_bytes(const pb200_model * m) { return m ? m->weight_b
 
 int pb200_model_tensor_device(pb200_model * m, const char * name, const void ** dev_ptr, size_t * nbytes, int * type) {
     if (!m || !name || !dev_ptr || !nbytes) return PB200_EINVAL;
+    NOT_FOR_LAYER_LIST(m);
     bool is_f32 = false;
     float ** slot = nullptr;
     int64_t n_f32 = 0;
@@ -661,6 +612,7 @@ static int prefill_ubatch(pb200_model * m, const int32_t * tokens_host, const fl
 static const int PB200_N_UBATCH = 512;   // the reference's default n_ubatch (common/common.h): longer prompts go through in slices
 
 extern "C" int pb200_prefill(pb200_model * m, const int32_t * tokens_host, int32_t T, int32_t pos0, float * logits_host) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized) return PB200_ESTATE;
     if (!tokens_host || T <= 0 || pos0 < 0 || pos0 + T > m->hp.n_ctx) return PB200_EINVAL;
     if (!m->with_embd || m->l0 != 0) return PB200_ENOTSUP;   // whole prompts start at the embedding; pipeline shards: pb200_prefill_stage
@@ -676,13 +628,14 @@ extern "C" int pb200_prefill(pb200_model * m, const int32_t * tokens_host, int32
 // previous stage's hidden states [n_tokens][n_embd] f32 in device memory (left untouched); the result stays in pb200_prefill_hidden_device.
 extern "C" int pb200_prefill_stage(pb200_model * m, const int32_t * tokens_host, const float * hidden_in_dev, int32_t T, int32_t pos0, float * logits_host,
                                    int32_t synchronize) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized) return PB200_ESTATE;
     if (T <= 0 || T > PB200_N_UBATCH || pos0 < 0 || pos0 + T > m->hp.n_ctx) return PB200_EINVAL;
     if (m->with_embd ? !tokens_host : !hidden_in_dev) return PB200_EINVAL;
     if (logits_host && !synchronize) return PB200_EINVAL;   // host logits are read back at the synchronisation point
     return prefill_ubatch(m, tokens_host, hidden_in_dev, T, pos0, logits_host, synchronize != 0);
 }
-extern "C" float * pb200_prefill_hidden_device(pb200_model * m) { return (m && m->finalized) ? m->pf.x0 : nullptr; }
+extern "C" float * pb200_prefill_hidden_device(pb200_model * m) { return (m && m->finalized && !m->ll) ? m->pf.x0 : nullptr; }
 
 static int prefill_ubatch(pb200_model * m, const int32_t * tokens_host, const float * hidden_in_dev, int32_t T, int32_t pos0, float * logits_host, bool sync) {
     if (!m || !m->finalized) return PB200_ESTATE;
@@ -770,6 +723,7 @@ static int prefill_ubatch(pb200_model * m, const int32_t * tokens_host, const fl
 
 extern "C" {
 int pb200_kv_clear(pb200_model * m) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized) return PB200_ESTATE;
     cudaSetDevice(m->device);
     const size_t kvb = (size_t) m->n_seq * m->layers.size() * (size_t) m->hp.n_ctx * m->hp.n_head_kv * m->hp.head_dim * sizeof(__half);
@@ -823,6 +777,7 @@ __global__ void __launch_bounds__(1024) k_argmax(const float * __restrict__ x, i
 __global__ void k_advance_pos(int32_t * tp) { pdl_trigger(); pdl_wait(); tp[1] += 1; }
 
 int pb200_decode_async(pb200_model * m, int32_t token, int32_t pos) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized) return PB200_ESTATE;
     if (pos < 0 || pos >= m->hp.n_ctx || token < 0 || token >= m->hp.n_vocab) return PB200_EINVAL;
     cudaSetDevice(m->device);
@@ -832,6 +787,7 @@ int pb200_decode_async(pb200_model * m, int32_t token, int32_t pos) {
 }
 
 int pb200_decode(pb200_model * m, int32_t token, int32_t pos, float * logits_host) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized) return PB200_ESTATE;
     if (pos < 0 || pos >= m->hp.n_ctx || token < 0 || token >= m->hp.n_vocab) return PB200_EINVAL;
     cudaSetDevice(m->device);
@@ -852,12 +808,14 @@ int pb200_decode(pb200_model * m, int32_t token, int32_t pos, float * logits_hos
 
 // ---- several sequences in flight (prima's ring keeps every stage busy with a different token, src/llama.cpp:17825-18029, 18299-18387) ----
 int pb200_model_set_n_seq(pb200_model * m, int n_seq) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || n_seq < 1 || n_seq > 64) return PB200_EINVAL;
     if (m->finalized) return PB200_ESTATE;
     m->n_seq = n_seq;
     return 0;
 }
 int pb200_decode_seq_async(pb200_model * m, int seq, int32_t token, int32_t pos) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized) return PB200_ESTATE;
     if (seq < 0 || seq >= m->n_seq || pos < 0 || pos >= m->hp.n_ctx || token < 0 || token >= m->hp.n_vocab) return PB200_EINVAL;
     cudaSetDevice(m->device);
@@ -868,6 +826,7 @@ int pb200_decode_seq_async(pb200_model * m, int seq, int32_t token, int32_t pos)
 // token and position of the slot are ALREADY in device memory (pb200_token_device: written by the previous stage's hand-off or by
 // pb200_argmax_seq); nothing crosses the host.  advance_pos: bump the slot's position afterwards for its next step.
 int pb200_step_seq_dev(pb200_model * m, int seq, int advance_pos) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized) return PB200_ESTATE;
     if (seq < 0 || seq >= m->n_seq) return PB200_EINVAL;
     cudaSetDevice(m->device);
@@ -880,6 +839,7 @@ int pb200_step_seq_dev(pb200_model * m, int seq, int advance_pos) {
     return 0;
 }
 int pb200_set_tokpos_seq(pb200_model * m, int seq, int32_t token, int32_t pos) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized) return PB200_ESTATE;
     if (seq < 0 || seq >= m->n_seq) return PB200_EINVAL;
     cudaSetDevice(m->device);
@@ -888,6 +848,7 @@ int pb200_set_tokpos_seq(pb200_model * m, int seq, int32_t token, int32_t pos) {
 }
 // greedy token of the slot's logits -> sample_dev[seq] (and, when this shard also holds the embedding, straight into the slot's token)
 int pb200_argmax_seq(pb200_model * m, int seq, int feed_back) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized || !m->with_head) return PB200_ESTATE;
     if (seq < 0 || seq >= m->n_seq) return PB200_EINVAL;
     cudaSetDevice(m->device);
@@ -901,8 +862,8 @@ int pb200_argmax_seq(pb200_model * m, int seq, int feed_back) {
     return (int) cudaLaunchKernelEx(&cfg, k_argmax, (const float *) m->logits, (int) m->hp.n_vocab, m->sample_dev + seq,
                                     (int32_t *) (feed_back && m->with_embd ? m->tokpos_dev + 4 * seq : nullptr));
 }
-int32_t * pb200_token_device(pb200_model * m, int seq) { return (m && seq >= 0 && seq < m->n_seq) ? m->tokpos_dev + 4 * seq : nullptr; }
-int32_t * pb200_sample_device(pb200_model * m, int seq) { return (m && seq >= 0 && seq < m->n_seq) ? m->sample_dev + seq : nullptr; }
+int32_t * pb200_token_device(pb200_model * m, int seq) { return (m && !m->ll && seq >= 0 && seq < m->n_seq) ? m->tokpos_dev + 4 * seq : nullptr; }
+int32_t * pb200_sample_device(pb200_model * m, int seq) { return (m && !m->ll && seq >= 0 && seq < m->n_seq) ? m->sample_dev + seq : nullptr; }
 
 int pb200_synchronize(pb200_model * m) {
     if (!m) return PB200_EINVAL;
@@ -915,12 +876,14 @@ float * pb200_hidden_in_device(pb200_model * m) { return m ? m->x_in : nullptr; 
 float * pb200_hidden_out_device(pb200_model * m) { return m ? m->x_out : nullptr; }
 void * pb200_stream(pb200_model * m) { return m ? (void *) m->stream : nullptr; }
 int pb200_get_hidden(pb200_model * m, float * hidden_host) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized || !hidden_host) return PB200_EINVAL;
     cudaSetDevice(m->device);
     CK(cudaStreamSynchronize(m->stream));
     return (int) cudaMemcpy(hidden_host, m->x_out, (size_t) m->hp.n_embd * 4, cudaMemcpyDeviceToHost);
 }
 int pb200_profile_step(pb200_model * m, int32_t token, int32_t pos, double * gemv_ms, int64_t * gemv_bytes, int32_t * gemv_launches, double * step_ms) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized) return PB200_ESTATE;
     if (pos < 0 || pos >= m->hp.n_ctx || token < 0 || token >= m->hp.n_vocab) return PB200_EINVAL;
     cudaSetDevice(m->device);
@@ -953,6 +916,7 @@ int pb200_profile_step(pb200_model * m, int32_t token, int32_t pos, double * gem
     return 0;
 }
 int pb200_set_hidden(pb200_model * m, const float * hidden_host) {
+    NOT_FOR_LAYER_LIST(m);
     if (!m || !m->finalized || !hidden_host) return PB200_EINVAL;
     cudaSetDevice(m->device);
     CK(cudaStreamSynchronize(m->stream));
@@ -960,6 +924,7 @@ int pb200_set_hidden(pb200_model * m, const float * hidden_host) {
 }
 // debugging / white-box tests: copy a named internal activation buffer of the LAST step to the host
 int pb200_debug_read(pb200_model * m, const char * name, float * host, int64_t n) {
+    if (m && m->ll && m->finalized && name && host) return ll_debug_read(m, name, host, n);
     if (!m || !m->finalized || !name || !host) return PB200_EINVAL;
     cudaSetDevice(m->device);
     CK(cudaStreamSynchronize(m->stream));

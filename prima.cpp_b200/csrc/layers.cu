@@ -1,0 +1,893 @@
+// prima.cpp_b200/csrc/layers.cu — the engine of the layer-list family (arch.h): a configuration file lists the layers, every layer has
+// a sequence mixer (windowed attention with kept first tokens, or a Mamba-2 state-space mixer) and an optional gated feed-forward,
+// weights are dense f32 / bf16 matrices.  It lives behind the same model object and C ABI as the k-quant transformer engine
+// (engine.cu): pb200_model_set_tensor / _finalize / _free, sequence slots, pb200_decode / pb200_prefill on slot 0, device arg-max —
+// plus the ragged batch step (pb200_batch_step) that the scheduler drives.
+//
+// State manager: every sequence slot owns one arena of constant size.  Per layer RUN (a layer inside a repeated block runs several
+// times per token and each pass has its own state): attention -> K and V rows (positions below keep_first at their own row, later ones
+// in a ring as long as the window), Mamba-2 -> the last taps-1 convolution inputs and the fp32 state [heads][state][vdim].  A slot's
+// arena is zeroed when it is handed out, so a reused slot starts like a new one.
+//
+// Precision: the residual stream, norms, attention scores / weights, recurrent state and everything that feeds the recurrence are
+// fp32 in both compute types; with T_BF16 only the two operands of a dense product are bf16 (fp32 accumulation).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "arch.h"
+#include "json.h"
+#include "layers.h"
+#include "model.h"
+
+extern std::atomic<uint64_t> g_launches;
+
+#define CK(expr)                  \
+    do {                          \
+        int _e = (int) (expr);    \
+        if (_e != 0) return _e;   \
+    } while (0)
+
+namespace pb {
+
+enum : int { MIX_ATTENTION = 0, MIX_MAMBA2 = 1 };
+
+struct DenseW {           // row-major [N][K] in the model's compute type
+    void * data = nullptr;
+    int64_t N = 0, K = 0;
+    std::vector<uint8_t> filled;   // one flag per row block a checkpoint tensor fills (fused projections are filled by several tensors)
+};
+struct VecF {             // small fp32 parameter (norm weights, convolution taps, decay / step parameters)
+    float * data = nullptr;
+    int64_t n = 0;
+    bool filled = false;
+};
+
+struct LLayer {
+    int kind = MIX_ATTENTION;
+    AttnParams att;
+    Mamba2Params ssm;
+    int ff = 0;                        // 0: the layer has no feed-forward
+    VecF norm1, norm1b, norm2, norm2b;
+    DenseW qkvg, out;                  // attention: fused q | k | v | gate projection; `out` is the mixer's output projection of either kind
+    DenseW in;                         // mamba2 input projection  z | x | B | C | dt
+    VecF conv_w, conv_b, dt_bias, A_log, D, gnorm;
+    DenseW gateup, down;               // feed-forward: fused gate | up
+};
+
+struct LRun {
+    int layer = 0;
+    int pass = -1;            // >= 0: this run opens pass `pass` of the repeated block (input mix + step vector come first)
+    int64_t state_off = 0;    // floats from the slot's arena base
+};
+
+// where a checkpoint tensor goes
+struct TensorPlace {
+    DenseW * mat = nullptr;   // rows [row0, row0 + rows) of a matrix with `cols` columns ...
+    int64_t row0 = 0, rows = 0, cols = 0;
+    int part = 0;             // index into mat->filled
+    VecF * vec = nullptr;     // ... or a whole fp32 vector of n elements
+    int64_t n = 0;
+};
+
+struct LayerList {
+    const ArchEntry * arch = nullptr;
+    int ctype = T_BF16;       // compute type: operand type of the dense products
+    int width = 0, vocab = 0;
+    float eps = 1e-6f, logit_scale = 1.f;
+    std::vector<LLayer> layers;
+    std::vector<LRun> runs;
+    // repeated block
+    int loop_start = 0, loop_stop = 0, loop_times = 0;
+    DenseW loop_in;
+    VecF loop_step;
+    DenseW embed, head;
+    VecF final_norm;
+    // state manager
+    int n_ctx = 0, n_seq = 0;
+    bool ctx_limited = false;       // some cache holds every position: a sequence cannot outgrow n_ctx
+    int64_t slot_floats = 0;
+    float * state = nullptr;
+    std::vector<int32_t> seq_len;   // -1: free
+    // batch scratch (grown on demand)
+    int capT = 0, capW = 0;
+    float *x = nullptr, *x0 = nullptr, *xalt = nullptr, *big = nullptr, *msub = nullptr, *xbc = nullptr, *yssm = nullptr, *logits = nullptr;
+    void *act = nullptr, *act2 = nullptr, *actw = nullptr;
+    int32_t *meta_dev = nullptr, *meta_host = nullptr, *greedy_dev = nullptr, *greedy_host = nullptr;
+    float * logits_host = nullptr;
+    size_t meta_cap = 0, logits_host_cap = 0;
+    std::vector<void *> scratch;
+    // white-box tap: residual stream after every layer run of the last batch
+    bool tap_on = false;
+    float * tap = nullptr;
+    int64_t tap_floats = 0, tap_cap = 0;
+    int tap_T = 0;
+    int64_t weight_bytes = 0;
+    std::vector<int> rows_tmp;      // logits row of the caller (or -(entry+1) for a greedy row) per wanted row of the last sub-batch
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// Vamidra: configuration keys and tensor names
+static int vamidra_configure(const Json & cfg, LayerList & ll, std::string & err) {
+    ll.width = (int) cfg.integer("width", 0);
+    ll.vocab = (int) cfg.integer("vocab", 0);
+    ll.logit_scale = (float) cfg.number("logit_scale", 1.0);
+    if (const Json * nrm = cfg.get("norm")) ll.eps = (float) nrm->number("eps", 1e-6);
+    const Json * layers = cfg.get("layers");
+    if (ll.width <= 0 || ll.vocab <= 0 || !layers || layers->kind != Json::ARR || layers->arr.empty()) { err = "width, vocab and layers are required"; return PB200_EINVAL; }
+    for (const Json & jl : layers->arr) {
+        LLayer L;
+        const std::string type = jl.string("type");
+        const Json * mx = jl.get("mixer");
+        if (!mx || mx->kind != Json::OBJ) { err = "layer without mixer"; return PB200_EINVAL; }
+        if (type == "attention") {
+            L.kind = MIX_ATTENTION;
+            AttnParams & a = L.att;
+            a.heads = (int) mx->integer("heads", 0);
+            a.kv_heads = (int) mx->integer("kv_heads", a.heads);
+            a.dim = (int) mx->integer("dim", 0);
+            a.vdim = (int) mx->integer("vdim", a.dim);
+            a.scale = (float) mx->number("scale", a.dim > 0 ? 1.0 / std::sqrt((double) a.dim) : 1.0);
+            a.softcap = (float) mx->number("softcap", 0.0);
+            a.window = 0;
+            a.keep_first = 0;
+            if (const Json * mk = mx->get("mask")) {
+                if (mk->kind == Json::OBJ) {
+                    a.window = (int) std::min<long long>(mk->integer("size", 0), 1 << 30);
+                    a.keep_first = (int) std::min<long long>(std::max<long long>(mk->integer("keep_first", 0), 0), 1 << 30);
+                }
+            }
+            if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || a.vdim > 256) { err = "attention sizes"; return PB200_EINVAL; }
+        } else if (type == "mamba2") {
+            L.kind = MIX_MAMBA2;
+            Mamba2Params & p = L.ssm;
+            p.heads = (int) mx->integer("heads", 0);
+            p.vdim = (int) mx->integer("vdim", 0);
+            p.state = (int) mx->integer("state", 0);
+            p.groups = (int) mx->integer("groups", 1);
+            p.conv = (int) mx->integer("conv", 1);
+            p.norm_groups = (int) mx->integer("norm_groups", 1);
+            if (p.heads <= 0 || p.vdim <= 0 || p.state <= 0 || p.groups <= 0 || p.heads % p.groups || p.conv < 1 || p.norm_groups <= 0 ||
+                (p.heads * p.vdim) % p.norm_groups) { err = "mamba2 sizes"; return PB200_EINVAL; }
+        } else {
+            err = "unknown layer type '" + type + "'";
+            return PB200_ENOTSUP;
+        }
+        const Json * mlp = jl.get("mlp");
+        if (mlp && mlp->kind == Json::OBJ) {
+            const std::string kind = mlp->string("kind", "dense");
+            if (kind != "dense") { err = "unknown feed-forward kind '" + kind + "'"; return PB200_ENOTSUP; }
+            L.ff = (int) mlp->integer("ff", 0);
+            if (L.ff <= 0) { err = "feed-forward size"; return PB200_EINVAL; }
+        }
+        ll.layers.push_back(std::move(L));
+    }
+    const int nl = (int) ll.layers.size();
+    ll.loop_times = 0;
+    if (const Json * lp = cfg.get("loop")) {
+        if (lp->kind == Json::OBJ) {
+            ll.loop_start = (int) lp->integer("start", 0);
+            ll.loop_stop = (int) lp->integer("stop", 0);
+            ll.loop_times = (int) lp->integer("times", 1);
+            if (ll.loop_start < 0 || ll.loop_stop > nl || ll.loop_start >= ll.loop_stop || ll.loop_times < 1) { err = "loop range"; return PB200_EINVAL; }
+        }
+    }
+    // order of layer runs: layers before the block once, the block `times` times in a row, the rest once
+    for (int i = 0; i < nl;) {
+        if (ll.loop_times > 0 && i == ll.loop_start) {
+            for (int t = 0; t < ll.loop_times; t++)
+                for (int k = ll.loop_start; k < ll.loop_stop; k++) {
+                    LRun r;
+                    r.layer = k;
+                    r.pass = k == ll.loop_start ? t : -1;
+                    ll.runs.push_back(r);
+                }
+            i = ll.loop_stop;
+        } else {
+            LRun r;
+            r.layer = i++;
+            ll.runs.push_back(r);
+        }
+    }
+    return 0;
+}
+
+static bool vamidra_resolve(LayerList & ll, const std::string & name, TensorPlace & o) {
+    const int64_t W = ll.width;
+    auto mat = [&](DenseW & m, int64_t row0, int64_t rows, int64_t cols, int part) { o.mat = &m; o.row0 = row0; o.rows = rows; o.cols = cols; o.part = part; return true; };
+    auto vec = [&](VecF & v, int64_t n) { o.vec = &v; o.n = n; return true; };
+    if (name == "embed") return mat(ll.embed, 0, ll.vocab, W, 0);
+    if (name == "head") return mat(ll.head, 0, ll.vocab, W, 0);
+    if (name == "final.norm") return vec(ll.final_norm, W);
+    if (name == "loop.in") return ll.loop_times > 0 && mat(ll.loop_in, 0, W, 2 * W, 0);
+    if (name == "loop.step") return ll.loop_times > 0 && vec(ll.loop_step, (int64_t) ll.loop_times * W);
+    int il = -1, used = 0;
+    if (sscanf(name.c_str(), "l%d.%n", &il, &used) != 1 || used <= 0 || il < 0 || il >= (int) ll.layers.size()) return false;
+    LLayer & L = ll.layers[il];
+    const std::string w = name.substr((size_t) used);
+    if (w == "norm1") return vec(L.norm1, W);
+    if (w == "norm1b") return vec(L.norm1b, W);
+    if (L.ff > 0) {
+        if (w == "norm2") return vec(L.norm2, W);
+        if (w == "norm2b") return vec(L.norm2b, W);
+        if (w == "mlp.gate") return mat(L.gateup, 0, L.ff, W, 0);
+        if (w == "mlp.up") return mat(L.gateup, L.ff, L.ff, W, 1);
+        if (w == "mlp.down") return mat(L.down, 0, W, L.ff, 0);
+    }
+    if (L.kind == MIX_ATTENTION) {
+        const AttnParams & a = L.att;
+        const int64_t QD = (int64_t) a.heads * a.dim, KD = (int64_t) a.kv_heads * a.dim, VD = (int64_t) a.kv_heads * a.vdim;
+        if (w == "mix.q") return mat(L.qkvg, 0, QD, W, 0);
+        if (w == "mix.k") return mat(L.qkvg, QD, KD, W, 1);
+        if (w == "mix.v") return mat(L.qkvg, QD + KD, VD, W, 2);
+        if (w == "mix.g") return mat(L.qkvg, QD + KD + VD, a.heads, W, 3);
+        if (w == "mix.o") return mat(L.out, 0, W, (int64_t) a.heads * a.vdim, 0);
+    } else {
+        const Mamba2Params & p = L.ssm;
+        if (w == "mix.in") return mat(L.in, 0, mamba2_in_cols(p), W, 0);
+        if (w == "mix.conv") return vec(L.conv_w, (int64_t) mamba2_conv_channels(p) * p.conv);
+        if (w == "mix.conv.b") return vec(L.conv_b, mamba2_conv_channels(p));
+        if (w == "mix.dt_bias") return vec(L.dt_bias, p.heads);
+        if (w == "mix.A_log") return vec(L.A_log, p.heads);
+        if (w == "mix.D") return vec(L.D, p.heads);
+        if (w == "mix.norm") return vec(L.gnorm, mamba2_inner(p));
+        if (w == "mix.o") return mat(L.out, 0, W, mamba2_inner(p), 0);
+    }
+    return false;
+}
+
+static const ArchEntry g_archs[] = {
+    {"llama", ARCH_KQUANT, 0, nullptr, nullptr},
+    {"qwen2", ARCH_KQUANT, 2, nullptr, nullptr},
+    {"Vamidra", ARCH_LAYERS, 0, vamidra_configure, vamidra_resolve},
+};
+int arch_count() { return (int) (sizeof(g_archs) / sizeof(g_archs[0])); }
+const ArchEntry * arch_at(int i) { return (i >= 0 && i < arch_count()) ? &g_archs[i] : nullptr; }
+const ArchEntry * arch_find(const char * name) {
+    if (!name) return nullptr;
+    for (const ArchEntry & a : g_archs)
+        if (strcmp(a.name, name) == 0) return &a;
+    return nullptr;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+static size_t esize(int type) { return type == T_BF16 ? 2 : 4; }
+
+// every matrix / vector of the model with its size: allocation, completeness check, synthetic fill
+template <typename FM, typename FV>
+static void for_each_param(LayerList & ll, FM && fm, FV && fv) {
+    const int64_t W = ll.width;
+    fm(ll.embed, (int64_t) ll.vocab, W, 1);
+    fm(ll.head, (int64_t) ll.vocab, W, 1);
+    fv(ll.final_norm, W, 0);
+    if (ll.loop_times > 0) { fm(ll.loop_in, W, 2 * W, 1); fv(ll.loop_step, (int64_t) ll.loop_times * W, 1); }
+    for (LLayer & L : ll.layers) {
+        fv(L.norm1, W, 0); fv(L.norm1b, W, 0);
+        if (L.kind == MIX_ATTENTION) {
+            fm(L.qkvg, attn_qkvg_cols(L.att), W, 4);
+            fm(L.out, W, (int64_t) L.att.heads * L.att.vdim, 1);
+        } else {
+            const Mamba2Params & p = L.ssm;
+            fm(L.in, mamba2_in_cols(p), W, 1);
+            fv(L.conv_w, (int64_t) mamba2_conv_channels(p) * p.conv, 2); fv(L.conv_b, mamba2_conv_channels(p), 1);
+            fv(L.dt_bias, p.heads, 3); fv(L.A_log, p.heads, 4); fv(L.D, p.heads, 0); fv(L.gnorm, mamba2_inner(p), 0);
+            fm(L.out, W, mamba2_inner(p), 1);
+        }
+        if (L.ff > 0) {
+            fv(L.norm2, W, 0); fv(L.norm2b, W, 0);
+            fm(L.gateup, 2 * (int64_t) L.ff, W, 2);
+            fm(L.down, W, L.ff, 1);
+        }
+    }
+}
+
+static int ll_alloc_params(pb200_model * m) {
+    LayerList & ll = *m->ll;
+    int rc = 0;
+    int64_t bytes = 0;
+    for_each_param(
+        ll,
+        [&](DenseW & d, int64_t N, int64_t K, int parts) {
+            if (rc) return;
+            d.N = N; d.K = K; d.filled.assign((size_t) parts, 0);
+            const size_t b = (size_t) N * K * esize(ll.ctype);
+            rc = m->alloc(&d.data, b + 16);
+            bytes += (int64_t) b;
+        },
+        [&](VecF & v, int64_t n, int) {
+            if (rc) return;
+            v.n = n; v.filled = false;
+            rc = m->alloc((void **) &v.data, (size_t) n * 4);
+            bytes += n * 4;
+        });
+    ll.weight_bytes = bytes;
+    return rc;
+}
+
+static void bf16_to_f32(const uint16_t * s, float * d, size_t n) {
+    for (size_t i = 0; i < n; i++) { const uint32_t b = (uint32_t) s[i] << 16; memcpy(d + i, &b, 4); }
+}
+static void f32_to_bf16(const float * s, uint16_t * d, size_t n) {   // round to nearest even
+    for (size_t i = 0; i < n; i++) {
+        uint32_t b;
+        memcpy(&b, s + i, 4);
+        if ((b & 0x7fffffffu) > 0x7f800000u) { d[i] = (uint16_t) ((b >> 16) | 0x40); continue; }
+        b += 0x7fffu + ((b >> 16) & 1u);
+        d[i] = (uint16_t) (b >> 16);
+    }
+}
+
+}  // namespace pb
+
+using namespace pb;
+
+// ---------------------------------------------------------------------------------------------------------------
+// entry points used by engine.cu's dispatch (the public ABI functions of the model object forward here when m->ll is set)
+int ll_set_tensor(pb200_model * m, const char * name, int type, const void * host, size_t nbytes) {
+    LayerList & ll = *m->ll;
+    if (m->finalized) return PB200_ESTATE;
+    if (type != T_F32 && type != T_BF16) return PB200_ENOTSUP;
+    TensorPlace pl;
+    if (!ll.arch->resolve(ll, name, pl)) return PB200_EINVAL;
+    const int64_t count = pl.mat ? pl.rows * pl.cols : pl.n;
+    if (nbytes != (size_t) count * esize(type)) return PB200_EINVAL;
+    cudaSetDevice(m->device);
+    const int dtype = pl.mat ? ll.ctype : T_F32;
+    std::vector<uint8_t> conv;
+    const void * src = host;
+    if (type != dtype) {
+        conv.resize((size_t) count * esize(dtype));
+        if (dtype == T_F32) bf16_to_f32((const uint16_t *) host, (float *) conv.data(), (size_t) count);
+        else f32_to_bf16((const float *) host, (uint16_t *) conv.data(), (size_t) count);
+        src = conv.data();
+    }
+    if (pl.mat) {
+        if (pl.cols != pl.mat->K || pl.row0 + pl.rows > pl.mat->N) return PB200_EINVAL;
+        CK(cudaMemcpy((uint8_t *) pl.mat->data + (size_t) pl.row0 * pl.cols * esize(dtype), src, (size_t) count * esize(dtype), cudaMemcpyHostToDevice));
+        pl.mat->filled[(size_t) pl.part] = 1;
+    } else {
+        if (pl.n != pl.vec->n) return PB200_EINVAL;
+        CK(cudaMemcpy(pl.vec->data, src, (size_t) count * 4, cudaMemcpyHostToDevice));
+        pl.vec->filled = true;
+    }
+    return 0;
+}
+
+namespace {
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+template <typename OT>
+__global__ void k_fill_uniform(OT * p, int64_t n, float base, float half_range, uint64_t seed) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float u = (float) (mix64(seed + (uint64_t) i * 0x9E3779B97F4A7C15ull) >> 40) * (1.0f / 16777216.0f);
+    const float v = base + half_range * (2.f * u - 1.f);
+    if constexpr (sizeof(OT) == 2) p[i] = __float2bfloat16_rn(v); else p[i] = v;
+}
+}  // namespace
+
+// random weights generated on the device (benchmarks without a checkpoint): matrices uniform with standard deviation ~ 1/sqrt(K)
+int ll_synth(pb200_model * m, uint64_t seed) {
+    LayerList & ll = *m->ll;
+    if (m->finalized) return PB200_ESTATE;
+    cudaSetDevice(m->device);
+    uint64_t sd = seed * 0x100000001B3ull + 17;
+    int rc = 0;
+    for_each_param(
+        ll,
+        [&](DenseW & d, int64_t N, int64_t K, int) {
+            if (rc) return;
+            const int64_t n = N * K;
+            const float hr = 1.7320508f / sqrtf((float) K);
+            if (ll.ctype == T_BF16) k_fill_uniform<__nv_bfloat16><<<(unsigned) ((n + 255) / 256), 256, 0, m->stream>>>((__nv_bfloat16 *) d.data, n, 0.f, hr, ++sd);
+            else k_fill_uniform<float><<<(unsigned) ((n + 255) / 256), 256, 0, m->stream>>>((float *) d.data, n, 0.f, hr, ++sd);
+            rc = (int) cudaGetLastError();
+            std::fill(d.filled.begin(), d.filled.end(), 1);
+        },
+        [&](VecF & v, int64_t n, int kind) {   // kind 0: around one, 1: around zero, 2: convolution taps, 3: dt bias, 4: log of the decay rate
+            if (rc) return;
+            const float base = kind == 0 ? 1.f : kind == 3 ? -2.f : kind == 4 ? 0.5f : 0.f;
+            const float hr = kind == 0 ? 0.05f : kind == 1 ? 0.02f : kind == 2 ? 0.5f : 1.f;
+            k_fill_uniform<float><<<(unsigned) ((n + 255) / 256), 256, 0, m->stream>>>(v.data, n, base, hr, ++sd);
+            rc = (int) cudaGetLastError();
+            v.filled = true;
+        });
+    if (rc) return rc;
+    return (int) cudaStreamSynchronize(m->stream);
+}
+
+int ll_finalize(pb200_model * m) {
+    LayerList & ll = *m->ll;
+    if (m->finalized) return 0;
+    cudaSetDevice(m->device);
+    bool complete = true;
+    for_each_param(
+        ll, [&](DenseW & d, int64_t, int64_t, int) { for (uint8_t f : d.filled) complete = complete && f; },
+        [&](VecF & v, int64_t, int) { complete = complete && v.filled; });
+    if (!complete) return PB200_ESTATE;
+    // state arena layout of one slot
+    int64_t off = 0;
+    ll.ctx_limited = false;
+    for (LRun & r : ll.runs) {
+        LLayer & L = ll.layers[(size_t) r.layer];
+        r.state_off = off;
+        if (L.kind == MIX_ATTENTION) {
+            L.att.cache_rows = attn_cache_rows(L.att.window, L.att.keep_first, ll.n_ctx);
+            if (L.att.cache_rows >= ll.n_ctx) ll.ctx_limited = true;
+            off += (int64_t) L.att.cache_rows * L.att.kv_heads * (L.att.dim + L.att.vdim);
+        } else {
+            off += (int64_t) (L.ssm.conv - 1) * mamba2_conv_channels(L.ssm) + (int64_t) L.ssm.heads * L.ssm.state * L.ssm.vdim;
+        }
+        off = (off + 3) / 4 * 4;
+    }
+    ll.slot_floats = std::max<int64_t>(off, 4);
+    if (ll.n_seq <= 0) {   // as many slots as 8 GiB of state hold, between 4 and 64
+        const int64_t fit = (int64_t) (8ll << 30) / (ll.slot_floats * 4);
+        ll.n_seq = (int) std::min<int64_t>(64, std::max<int64_t>(4, fit));
+    }
+    CK(m->alloc((void **) &ll.state, (size_t) ll.slot_floats * 4 * (size_t) ll.n_seq));
+    CK(cudaMemset(ll.state, 0, (size_t) ll.slot_floats * 4 * (size_t) ll.n_seq));
+    ll.seq_len.assign((size_t) ll.n_seq, -1);
+    m->n_seq = ll.n_seq;
+    m->weight_bytes = ll.weight_bytes;
+    m->finalized = true;
+    return 0;
+}
+
+void ll_free(pb200_model * m) {
+    LayerList * ll = m->ll;
+    if (!ll) return;
+    for (void * p : ll->scratch) cudaFree(p);
+    if (ll->meta_dev) cudaFree(ll->meta_dev);
+    if (ll->meta_host) cudaFreeHost(ll->meta_host);
+    if (ll->greedy_host) cudaFreeHost(ll->greedy_host);
+    if (ll->logits_host) cudaFreeHost(ll->logits_host);
+    if (ll->tap) cudaFree(ll->tap);
+    delete ll;
+    m->ll = nullptr;
+}
+
+// ---- sequence slots ----
+int ll_seq_alloc(pb200_model * m) {
+    LayerList & ll = *m->ll;
+    if (!m->finalized) return PB200_ESTATE;
+    for (int s = 0; s < ll.n_seq; s++)
+        if (ll.seq_len[(size_t) s] < 0) {
+            cudaSetDevice(m->device);
+            // a slot that is handed out again starts from the empty state: zero convolution inputs, zero recurrent state, no cached keys
+            if (cudaMemsetAsync(ll.state + (int64_t) s * ll.slot_floats, 0, (size_t) ll.slot_floats * 4, m->stream) != cudaSuccess) return PB200_ENOMEM;
+            ll.seq_len[(size_t) s] = 0;
+            return s;
+        }
+    return PB200_ENOMEM;
+}
+int ll_seq_free(pb200_model * m, int slot) {
+    LayerList & ll = *m->ll;
+    if (slot < 0 || slot >= ll.n_seq || ll.seq_len[(size_t) slot] < 0) return PB200_EINVAL;
+    ll.seq_len[(size_t) slot] = -1;
+    return 0;
+}
+int ll_seq_length(pb200_model * m, int slot) {
+    LayerList & ll = *m->ll;
+    if (slot < 0 || slot >= ll.n_seq) return PB200_EINVAL;
+    return ll.seq_len[(size_t) slot];
+}
+
+// ---- scratch ----
+static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
+    LayerList & ll = *m->ll;
+    if (T > ll.capT || nW > ll.capW) {
+        CK(cudaStreamSynchronize(m->stream));
+        for (void * p : ll.scratch) cudaFree(p);
+        ll.scratch.clear();
+        const int cT = std::max(T, ll.capT), cW = std::max(nW, ll.capW);
+        ll.capT = ll.capW = 0;
+        int64_t maxact = ll.width, maxbig = ll.width, maxch = 1, maxinner = 1;
+        for (const LLayer & L : ll.layers) {
+            if (L.kind == MIX_ATTENTION) {
+                maxact = std::max<int64_t>(maxact, (int64_t) L.att.heads * L.att.vdim);
+                maxbig = std::max<int64_t>(maxbig, attn_qkvg_cols(L.att));
+            } else {
+                maxact = std::max<int64_t>(maxact, mamba2_inner(L.ssm));
+                maxbig = std::max<int64_t>(maxbig, mamba2_in_cols(L.ssm));
+                maxch = std::max<int64_t>(maxch, mamba2_conv_channels(L.ssm));
+                maxinner = std::max<int64_t>(maxinner, mamba2_inner(L.ssm));
+            }
+            maxact = std::max<int64_t>(maxact, L.ff);
+            maxbig = std::max<int64_t>(maxbig, 2 * (int64_t) L.ff);
+        }
+        auto grab = [&](void ** p, size_t bytes) -> int {
+            cudaError_t e = cudaMalloc(p, (bytes + 255) / 256 * 256 + 256);
+            if (e != cudaSuccess) return (int) e;
+            ll.scratch.push_back(*p);
+            return 0;
+        };
+        const size_t W = (size_t) ll.width, t = (size_t) cT, es = esize(ll.ctype);
+        CK(grab((void **) &ll.x, t * W * 4)); CK(grab((void **) &ll.x0, t * W * 4)); CK(grab((void **) &ll.xalt, t * W * 4));
+        CK(grab((void **) &ll.msub, t * W * 4));
+        CK(grab((void **) &ll.big, t * (size_t) maxbig * 4));
+        CK(grab((void **) &ll.xbc, t * (size_t) maxch * 4));
+        CK(grab((void **) &ll.yssm, t * (size_t) maxinner * 4));
+        CK(grab(&ll.act, t * (size_t) maxact * es));
+        CK(grab(&ll.act2, t * W * es));
+        CK(grab(&ll.actw, (size_t) cW * W * es));
+        CK(grab((void **) &ll.logits, (size_t) cW * (size_t) ll.vocab * 4));
+        CK(grab((void **) &ll.greedy_dev, (size_t) cW * 4));
+        if (ll.greedy_host) cudaFreeHost(ll.greedy_host);
+        ll.greedy_host = nullptr;
+        CK(cudaMallocHost((void **) &ll.greedy_host, (size_t) cW * 4));
+        ll.capT = cT; ll.capW = cW;
+    }
+    const size_t need_meta = (size_t) 2 * T + 3 * (size_t) nE + 1 + (size_t) nW + 64;
+    if (need_meta > ll.meta_cap) {
+        CK(cudaStreamSynchronize(m->stream));
+        if (ll.meta_dev) cudaFree(ll.meta_dev);
+        if (ll.meta_host) cudaFreeHost(ll.meta_host);
+        ll.meta_dev = nullptr; ll.meta_host = nullptr; ll.meta_cap = 0;
+        const size_t cap = need_meta * 2;
+        CK(cudaMalloc((void **) &ll.meta_dev, cap * 4));
+        CK(cudaMallocHost((void **) &ll.meta_host, cap * 4));
+        ll.meta_cap = cap;
+    }
+    const size_t need_lh = (size_t) std::max(nW, 1) * (size_t) ll.vocab;
+    if (need_lh > ll.logits_host_cap) {
+        CK(cudaStreamSynchronize(m->stream));
+        if (ll.logits_host) cudaFreeHost(ll.logits_host);
+        ll.logits_host = nullptr; ll.logits_host_cap = 0;
+        CK(cudaMallocHost((void **) &ll.logits_host, need_lh * 4));
+        ll.logits_host_cap = need_lh;
+    }
+    return 0;
+}
+
+// One homogeneous ragged batch through every layer run.  `prefill`: every entry starts at position 0 (keys and values are read from
+// the batch); otherwise every entry brings one token (keys and values come from the slot's cache).  Rows `want_dev[0..nW)` (token
+// indices of the batch) go through the final norm and the output head into logits rows lrow0 ...
+static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const int32_t * tokens_dev, const int32_t * want_dev, int nW, int lrow0) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
+    CK(launch_embed(ll.embed.data, ct, W, tokens_dev, T, ll.x, ll.x0, st));
+    float * x = ll.x, * xalt = ll.xalt;
+    if (ll.tap_on) {
+        const int64_t need = (int64_t) ll.runs.size() * T * W;
+        if (need > ll.tap_cap) {
+            CK(cudaStreamSynchronize(st));
+            if (ll.tap) cudaFree(ll.tap);
+            ll.tap = nullptr; ll.tap_cap = 0;
+            CK(cudaMalloc((void **) &ll.tap, (size_t) need * 4));
+            ll.tap_cap = need;
+        }
+        ll.tap_floats = need;
+        ll.tap_T = T;
+    }
+    for (size_t ir = 0; ir < ll.runs.size(); ir++) {
+        const LRun & r = ll.runs[ir];
+        LLayer & L = ll.layers[(size_t) r.layer];
+        if (r.pass >= 0) {
+            // x <- W_in [x ; x0] + step[pass]: two products over the halves of W_in, the second accumulating onto the first
+            CK(launch_cast(x, ll.act, ct, (int64_t) T * W, st));
+            CK(launch_cast(ll.x0, ll.act2, ct, (int64_t) T * W, st));
+            CK(launch_dense(ct, ll.act, W, ll.loop_in.data, 2 * W, xalt, W, T, W, W, ll.loop_step.data + (int64_t) r.pass * W, nullptr, 0, 1.f, st));
+            CK(launch_dense(ct, ll.act2, W, (const uint8_t *) ll.loop_in.data + (size_t) W * esize(ct), 2 * W, xalt, W, T, W, W, nullptr, xalt, W, 1.f, st));
+            std::swap(x, xalt);
+        }
+        float * sbase = ll.state + r.state_off;
+        CK(launch_layernorm(x, nullptr, L.norm1.data, ll.eps, ll.act, ct, T, W, st));
+        if (L.kind == MIX_ATTENTION) {
+            const AttnParams & a = L.att;
+            const int C = attn_qkvg_cols(a);
+            CK(launch_dense(ct, ll.act, W, L.qkvg.data, W, ll.big, C, T, C, W, nullptr, nullptr, 0, 1.f, st));
+            float * kc = sbase, * vc = sbase + (int64_t) a.cache_rows * a.kv_heads * a.dim;
+            CK(launch_attn_kv_store(ll.big, b, a, kc, vc, ll.slot_floats, st));
+            if (prefill) CK(launch_attn_window_prefill(ll.big, b, a, ll.act, ct, st));
+            else CK(launch_attn_window_decode(ll.big, b, a, kc, vc, ll.slot_floats, ll.act, ct, st));
+            CK(launch_dense(ct, ll.act, (int64_t) a.heads * a.vdim, L.out.data, (int64_t) a.heads * a.vdim, ll.msub, W, T, W, a.heads * a.vdim, nullptr, nullptr, 0,
+                            1.f, st));
+        } else {
+            const Mamba2Params & p = L.ssm;
+            const int U = mamba2_in_cols(p), inner = mamba2_inner(p);
+            CK(launch_dense(ct, ll.act, W, L.in.data, W, ll.big, U, T, U, W, nullptr, nullptr, 0, 1.f, st));
+            float * cs = sbase, * ss = sbase + (int64_t) (p.conv - 1) * mamba2_conv_channels(p);
+            CK(launch_mamba2_conv(ll.big, b, p, L.conv_w.data, L.conv_b.data, cs, ll.slot_floats, ll.xbc, st));
+            CK(launch_mamba2_scan(ll.big, ll.xbc, b, p, L.dt_bias.data, L.A_log.data, L.D.data, ss, ll.slot_floats, ll.yssm, st));
+            CK(launch_mamba2_gate_norm(ll.yssm, ll.big, p, L.gnorm.data, ll.eps, ll.act, ct, T, st));
+            CK(launch_dense(ct, ll.act, inner, L.out.data, inner, ll.msub, W, T, W, inner, nullptr, nullptr, 0, 1.f, st));
+        }
+        CK(launch_layernorm_residual(ll.msub, L.norm1b.data, ll.eps, x, T, W, st));
+        if (L.ff > 0) {
+            CK(launch_layernorm(x, nullptr, L.norm2.data, ll.eps, ll.act, ct, T, W, st));
+            CK(launch_dense(ct, ll.act, W, L.gateup.data, W, ll.big, 2 * L.ff, T, 2 * L.ff, W, nullptr, nullptr, 0, 1.f, st));
+            CK(launch_gelu_mul(ll.big, ll.act, ct, T, L.ff, st));
+            CK(launch_dense(ct, ll.act, L.ff, L.down.data, L.ff, ll.msub, W, T, W, L.ff, nullptr, nullptr, 0, 1.f, st));
+            CK(launch_layernorm_residual(ll.msub, L.norm2b.data, ll.eps, x, T, W, st));
+        }
+        if (ll.tap_on) CK(cudaMemcpyAsync(ll.tap + (int64_t) ir * T * W, x, (size_t) T * W * 4, cudaMemcpyDeviceToDevice, st));
+    }
+    if (nW > 0) {
+        CK(launch_layernorm(x, want_dev, ll.final_norm.data, ll.eps, ll.actw, ct, nW, W, st));
+        CK(launch_dense(ct, ll.actw, W, ll.head.data, W, ll.logits + (int64_t) lrow0 * ll.vocab, ll.vocab, nW, ll.vocab, W, nullptr, nullptr, 0, ll.logit_scale, st));
+    }
+    return 0;
+}
+
+// builds the device metadata of one homogeneous batch and runs it
+struct SubEntry { int slot, n, pos0; const int32_t * tokens; std::vector<std::pair<int, int>> want; /* (local token index, logits row) */ };
+
+static int ll_run_sub(pb200_model * m, std::vector<SubEntry> & es, bool prefill) {
+    LayerList & ll = *m->ll;
+    const int nE = (int) es.size();
+    if (!nE) return 0;
+    int T = 0, nW = 0, max_n = 0;
+    for (const SubEntry & e : es) { T += e.n; nW += (int) e.want.size(); max_n = std::max(max_n, e.n); }
+    CK(ll_reserve(m, T, nW, nE));
+    // meta layout: tokens[T] | entry_of[T] | slot[nE] | off[nE+1] | pos0[nE] | want[nW]
+    int32_t * h = ll.meta_host;
+    int32_t *h_tok = h, *h_ent = h + T, *h_slot = h + 2 * T, *h_off = h_slot + nE, *h_pos = h_off + nE + 1, *h_want = h_pos + nE;
+    int t = 0;
+    std::vector<int> lrows;
+    for (int i = 0; i < nE; i++) {
+        const SubEntry & e = es[(size_t) i];
+        h_slot[i] = e.slot; h_off[i] = t; h_pos[i] = e.pos0;
+        for (int k = 0; k < e.n; k++) { h_tok[t + k] = e.tokens[k]; h_ent[t + k] = i; }
+        t += e.n;
+    }
+    h_off[nE] = t;
+    // wanted rows: logits rows must be contiguous per call of the head product, so they are computed into a staging order and scattered on the host side
+    int w = 0;
+    for (int i = 0; i < nE; i++)
+        for (const auto & pr : es[(size_t) i].want) { h_want[w++] = h_off[i] + pr.first; lrows.push_back(pr.second); }
+    const size_t total = (size_t) (h_want + nW - h);
+    int32_t * d = ll.meta_dev;
+    CK(cudaMemcpyAsync(d, h, total * 4, cudaMemcpyHostToDevice, m->stream));
+    BatchView b;
+    b.n_entries = nE; b.n_tokens = T; b.max_n = max_n;
+    b.slot = d + 2 * T; b.off = b.slot + nE; b.pos0 = b.off + nE + 1; b.entry_of = d + T;
+    CK(ll_forward(m, b, prefill, d, d + (h_want - h), nW, 0));
+    if (nW > 0) CK(cudaMemcpyAsync(ll.logits_host, ll.logits, (size_t) nW * ll.vocab * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(cudaStreamSynchronize(m->stream));
+    // hand the rows to the caller's order
+    for (int i = 0; i < nE; i++) ll.seq_len[(size_t) es[(size_t) i].slot] = es[(size_t) i].pos0 + es[(size_t) i].n;
+    ll.rows_tmp.assign(lrows.begin(), lrows.end());
+    return 0;
+}
+
+int ll_batch_step(pb200_model * m, int n_entries, const pb200_batch_entry * entries, float * logits_out, int32_t * greedy_out) {
+    LayerList & ll = *m->ll;
+    if (!m->finalized) return PB200_ESTATE;
+    if (n_entries <= 0 || !entries) return PB200_EINVAL;
+    cudaSetDevice(m->device);
+    // validate, assign logits rows in entry order
+    std::vector<int> row_base((size_t) n_entries);
+    int rows = 0;
+    for (int i = 0; i < n_entries; i++) {
+        const pb200_batch_entry & e = entries[i];
+        if (e.seq < 0 || e.seq >= ll.n_seq || ll.seq_len[(size_t) e.seq] < 0 || e.n_tokens <= 0 || !e.tokens || e.n_want < 0 || (e.n_want > 0 && !e.want)) return PB200_EINVAL;
+        for (int j = 0; j < i; j++)
+            if (entries[j].seq == e.seq) return PB200_EINVAL;
+        for (int k = 0; k < e.n_tokens; k++)
+            if (e.tokens[k] < 0 || e.tokens[k] >= ll.vocab) return PB200_EINVAL;
+        for (int k = 0; k < e.n_want; k++)
+            if (e.want[k] < 0 || e.want[k] >= e.n_tokens) return PB200_EINVAL;
+        if (ll.ctx_limited && ll.seq_len[(size_t) e.seq] + e.n_tokens > ll.n_ctx) return PB200_EINVAL;
+        row_base[(size_t) i] = rows;
+        rows += e.n_want;
+    }
+    const bool want_greedy = greedy_out != nullptr;
+    const int V = ll.vocab;
+    auto deliver = [&](float * dst_rows_base) {
+        for (size_t k = 0; k < ll.rows_tmp.size(); k++) {
+            const int row = ll.rows_tmp[k];
+            if (row >= 0 && dst_rows_base) memcpy(dst_rows_base + (size_t) row * V, ll.logits_host + k * V, (size_t) V * 4);
+        }
+    };
+    // greedy tokens need the logits of every entry's last token; they ride as extra wanted rows (row index < 0 encodes the entry)
+    auto take_greedy = [&]() {
+        for (size_t k = 0; k < ll.rows_tmp.size(); k++) {
+            const int row = ll.rows_tmp[k];
+            if (row < 0) greedy_out[-row - 1] = ll.greedy_host[k];
+        }
+    };
+    auto run = [&](std::vector<SubEntry> & sub, bool prefill) -> int {
+        if (sub.empty()) return 0;
+        CK(ll_run_sub(m, sub, prefill));
+        if (want_greedy && !ll.rows_tmp.empty()) {
+            const int nW = (int) ll.rows_tmp.size();
+            CK(launch_argmax_rows(ll.logits, V, nW, ll.greedy_dev, m->stream));
+            CK(cudaMemcpyAsync(ll.greedy_host, ll.greedy_dev, (size_t) nW * 4, cudaMemcpyDeviceToHost, m->stream));
+            CK(cudaStreamSynchronize(m->stream));
+            take_greedy();
+        }
+        deliver(logits_out);
+        return 0;
+    };
+    // 1) entries that start a sequence go through together as one prompt batch
+    std::vector<SubEntry> sub;
+    for (int i = 0; i < n_entries; i++) {
+        const pb200_batch_entry & e = entries[i];
+        if (ll.seq_len[(size_t) e.seq] != 0) continue;
+        SubEntry s{e.seq, e.n_tokens, 0, e.tokens, {}};
+        for (int k = 0; k < e.n_want; k++) s.want.emplace_back(e.want[k], row_base[(size_t) i] + k);
+        if (want_greedy) s.want.emplace_back(e.n_tokens - 1, -(i + 1));
+        sub.push_back(std::move(s));
+    }
+    std::vector<char> done((size_t) n_entries, 0);
+    for (int i = 0; i < n_entries; i++) done[(size_t) i] = ll.seq_len[(size_t) entries[i].seq] == 0;
+    CK(run(sub, true));
+    // 2) entries that continue a sequence advance one token per pass, all of them in one batch per pass
+    int max_n = 0;
+    for (int i = 0; i < n_entries; i++)
+        if (!done[(size_t) i]) max_n = std::max(max_n, entries[i].n_tokens);
+    for (int k = 0; k < max_n; k++) {
+        sub.clear();
+        for (int i = 0; i < n_entries; i++) {
+            const pb200_batch_entry & e = entries[i];
+            if (done[(size_t) i] || e.n_tokens <= k) continue;
+            SubEntry s{e.seq, 1, ll.seq_len[(size_t) e.seq], e.tokens + k, {}};
+            for (int j = 0; j < e.n_want; j++)
+                if (e.want[j] == k) s.want.emplace_back(0, row_base[(size_t) i] + j);
+            if (want_greedy && k == e.n_tokens - 1) s.want.emplace_back(0, -(i + 1));
+            sub.push_back(std::move(s));
+        }
+        CK(run(sub, false));
+    }
+    return 0;
+}
+
+int ll_debug_read(pb200_model * m, const char * name, float * host, int64_t n) {
+    LayerList & ll = *m->ll;
+    cudaSetDevice(m->device);
+    CK(cudaStreamSynchronize(m->stream));
+    if (strcmp(name, "layers") == 0) {
+        if (!ll.tap || n > ll.tap_floats) return PB200_EINVAL;
+        return (int) cudaMemcpy(host, ll.tap, (size_t) n * 4, cudaMemcpyDeviceToHost);
+    }
+    return PB200_EINVAL;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+extern "C" {
+
+int pb200_arch_count(void) { return arch_count(); }
+const char * pb200_arch_name(int i) { const ArchEntry * a = arch_at(i); return a ? a->name : nullptr; }
+int pb200_arch_family(const char * name) { const ArchEntry * a = arch_find(name); return a ? a->family : -1; }
+
+pb200_model * pb200_model_create_from_config(const char * config_json, int compute_type, int device, int n_ctx, int n_seq) {
+    if (!config_json || (compute_type != T_F32 && compute_type != T_BF16) || n_ctx <= 0 || n_seq > 4096) return nullptr;
+    Json cfg;
+    if (!json_parse(config_json, cfg) || cfg.kind != Json::OBJ) return nullptr;
+    const ArchEntry * arch = arch_find(cfg.string("architecture").c_str());
+    if (!arch || arch->family != ARCH_LAYERS) return nullptr;
+    LayerList * ll = new LayerList();
+    ll->arch = arch;
+    ll->ctype = compute_type;
+    ll->n_ctx = n_ctx;
+    ll->n_seq = n_seq;
+    std::string err;
+    if (arch->configure(cfg, *ll, err) != 0) {
+        fprintf(stderr, "[pb200] %s configuration: %s\n", arch->name, err.c_str());
+        delete ll;
+        return nullptr;
+    }
+    if (cudaSetDevice(device) != cudaSuccess) { delete ll; return nullptr; }
+    pb200_model * m = new pb200_model();
+    m->ll = ll;
+    m->device = device;
+    m->with_embd = m->with_head = true;
+    m->hp.n_layer = (int32_t) ll->layers.size();
+    m->hp.n_embd = ll->width;
+    m->hp.n_vocab = ll->vocab;
+    m->hp.n_ctx = n_ctx;
+    m->l0 = 0;
+    m->l1 = m->hp.n_layer;
+    if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess) { delete ll; delete m; return nullptr; }
+    if (ll_alloc_params(m) != 0) { pb200_model_free(m); return nullptr; }
+    return m;
+}
+
+// config.json + model.safetensors of a directory -> finalized model.  A safetensors file is an 8-byte little-endian header length, a JSON
+// table name -> {dtype, shape, data_offsets}, then the tensor data; the file is mapped and every tensor handed to pb200_model_set_tensor.
+int pb200_model_load_dir(const char * dir, int compute_type, int device, int n_ctx, int n_seq, pb200_model ** out) {
+    if (!dir || !out) return PB200_EINVAL;
+    *out = nullptr;
+    const std::string d(dir);
+    std::string cfg_text;
+    {
+        FILE * f = fopen((d + "/config.json").c_str(), "rb");
+        if (!f) return PB200_EINVAL;
+        char buf[4096];
+        size_t n;
+        while ((n = fread(buf, 1, sizeof buf, f)) > 0) cfg_text.append(buf, n);
+        fclose(f);
+    }
+    Json cfg;
+    if (!json_parse(cfg_text, cfg) || cfg.kind != Json::OBJ) return PB200_EINVAL;
+    const ArchEntry * arch = arch_find(cfg.string("architecture").c_str());
+    if (!arch || arch->family != ARCH_LAYERS) return PB200_ENOTSUP;
+    pb200_model * m = pb200_model_create_from_config(cfg_text.c_str(), compute_type, device, n_ctx, n_seq);
+    if (!m) return PB200_EINVAL;
+    const int fd = open((d + "/model.safetensors").c_str(), O_RDONLY);
+    if (fd < 0) { pb200_model_free(m); return PB200_EINVAL; }
+    struct stat sb;
+    if (fstat(fd, &sb) != 0 || sb.st_size < 8) { close(fd); pb200_model_free(m); return PB200_EINVAL; }
+    const size_t fsz = (size_t) sb.st_size;
+    void * map = mmap(nullptr, fsz, PROT_READ, MAP_PRIVATE, fd, 0);
+    close(fd);
+    if (map == MAP_FAILED) { pb200_model_free(m); return PB200_EINVAL; }
+    const uint8_t * base = (const uint8_t *) map;
+    int rc = 0;
+    uint64_t hlen = 0;
+    memcpy(&hlen, base, 8);
+    Json hdr;
+    if (hlen > fsz - 8 || !JsonParser((const char *) base + 8, (size_t) hlen).parse(hdr) || hdr.kind != Json::OBJ) rc = PB200_EINVAL;
+    const uint8_t * data = base + 8 + hlen;
+    const size_t dsz = fsz - 8 - (size_t) hlen;
+    for (size_t i = 0; rc == 0 && i < hdr.obj.size(); i++) {
+        const std::string & name = hdr.obj[i].first;
+        const Json & t = hdr.obj[i].second;
+        if (name == "__metadata__") continue;
+        const std::string dt = t.string("dtype");
+        const Json * offs = t.get("data_offsets");
+        if (!offs || offs->kind != Json::ARR || offs->arr.size() != 2) { rc = PB200_EINVAL; break; }
+        const uint64_t lo = (uint64_t) offs->arr[0].num, hi = (uint64_t) offs->arr[1].num;
+        if (lo > hi || hi > dsz) { rc = PB200_EINVAL; break; }
+        const int type = dt == "BF16" ? T_BF16 : dt == "F32" ? T_F32 : -1;
+        if (type < 0) { rc = PB200_ENOTSUP; break; }
+        rc = pb200_model_set_tensor(m, name.c_str(), type, data + lo, (size_t) (hi - lo));
+        if (rc) fprintf(stderr, "[pb200] tensor '%s': %s\n", name.c_str(), pb200_error_string(rc));
+    }
+    munmap(map, fsz);
+    if (rc == 0) rc = pb200_model_finalize(m);
+    if (rc) { pb200_model_free(m); return rc; }
+    *out = m;
+    return 0;
+}
+
+int pb200_model_get_hparams(const pb200_model * m, pb200_hparams * out) {
+    if (!m || !out) return PB200_EINVAL;
+    *out = m->hp;
+    return 0;
+}
+int pb200_model_n_seq(const pb200_model * m) { return m ? m->n_seq : 0; }
+
+int pb200_seq_alloc(pb200_model * m) {
+    if (!m) return PB200_EINVAL;
+    if (!m->ll) return PB200_ENOTSUP;
+    return ll_seq_alloc(m);
+}
+int pb200_seq_free(pb200_model * m, int slot) {
+    if (!m) return PB200_EINVAL;
+    if (!m->ll) return PB200_ENOTSUP;
+    return ll_seq_free(m, slot);
+}
+int pb200_seq_length(pb200_model * m, int slot) {
+    if (!m) return PB200_EINVAL;
+    if (!m->ll) return PB200_ENOTSUP;
+    return ll_seq_length(m, slot);
+}
+int pb200_batch_step(pb200_model * m, int n_entries, const pb200_batch_entry * entries, float * logits_host, int32_t * greedy_host) {
+    if (!m) return PB200_EINVAL;
+    if (!m->ll) return PB200_ENOTSUP;
+    return ll_batch_step(m, n_entries, entries, logits_host, greedy_host);
+}
+int pb200_debug_tap_layers(pb200_model * m, int on) {
+    if (!m || !m->ll) return PB200_EINVAL;
+    m->ll->tap_on = on != 0;
+    return 0;
+}
+
+}  // extern "C"

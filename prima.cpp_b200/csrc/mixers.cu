@@ -1,0 +1,557 @@
+// prima.cpp_b200/csrc/mixers.cu — sequence mixers, norms and element-wise steps of the layer-list engine (declarations and the
+// semantics of every launcher: layers.h).  Everything here runs in fp32: scores, soft-cap, softmax weights, norms, the recurrent
+// state, decays and step sizes; only the value written for a following dense product is rounded to that product's operand type.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include <atomic>
+
+#include "layers.h"
+
+extern std::atomic<uint64_t> g_launches;
+
+namespace pb {
+namespace {
+
+__device__ __forceinline__ void put(float * p, int64_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void put(__nv_bfloat16 * p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float wmax(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// sum over the CTA (blockDim.x a multiple of 32, <= 1024); every thread gets the result; `red` is 33 floats of shared memory
+__device__ __forceinline__ float block_sum(float v, float * red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = wsum(v);
+    __syncthreads();   // red may still be read from a previous call
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float s = lane < nw ? red[lane] : 0.f;
+        s = wsum(s);
+        if (lane == 0) red[32] = s;
+    }
+    __syncthreads();
+    return red[32];
+}
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
+
+// ---------------------------------------------------------------------------------------------------------------
+template <typename WT>
+__global__ void k_embed(const WT * __restrict__ table, int width, const int32_t * __restrict__ tokens, float * __restrict__ x, float * __restrict__ x2) {
+    const int t = blockIdx.x;
+    const WT * row = table + (int64_t) tokens[t] * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v;
+        if constexpr (sizeof(WT) == 2) v = __bfloat162float(row[i]); else v = row[i];
+        x[(int64_t) t * width + i] = v;
+        if (x2) x2[(int64_t) t * width + i] = v;
+    }
+}
+
+template <typename OT>
+__global__ void k_cast(const float * __restrict__ x, OT * __restrict__ y, int64_t n) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) put(y, i, x[i]);
+}
+
+// layer norm with a weight and no bias; two passes over the row (mean, then the mean of squared deviations)
+template <typename OT, bool RESID>
+__global__ void __launch_bounds__(256) k_layernorm(const float * __restrict__ x, const int32_t * __restrict__ rows, const float * __restrict__ w, float eps,
+                                                   OT * __restrict__ y, float * __restrict__ xres, int width) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const float * in = x + (int64_t) (rows ? rows[r] : r) * width;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) s += in[i];
+    const float mean = block_sum(s, red) / (float) width;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float d = in[i] - mean; q = fmaf(d, d, q); }
+    const float var = block_sum(q, red) / (float) width;
+    const float inv = 1.f / sqrtf(var + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = (in[i] - mean) * inv * w[i];
+        if constexpr (RESID) xres[(int64_t) r * width + i] += v;
+        else put(y, (int64_t) r * width + i, v);
+    }
+}
+
+template <typename OT>
+__global__ void k_gelu_mul(const float * __restrict__ gu, OT * __restrict__ y, int n_tokens, int ff) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t) n_tokens * ff) return;
+    const int64_t t = i / ff, j = i - t * ff;
+    const float g = gu[t * 2 * ff + j], u = gu[t * 2 * ff + ff + j];
+    const float act = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    put(y, i, act * u);
+}
+
+__global__ void __launch_bounds__(256) k_argmax_rows(const float * __restrict__ x, int n, int32_t * __restrict__ out) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const float * row = x + (int64_t) blockIdx.x * n;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best) { best = v; bi = i; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int k = 1; k < (int) (blockDim.x >> 5); k++)
+            if (sv[k] > best || (sv[k] == best && si[k] < bi)) { best = sv[k]; bi = si[k]; }
+        out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// attention.  Cache row of position p: p itself below keep_first, else keep_first + (p - keep_first) mod ring.
+__device__ __forceinline__ int cache_row(int p, int keep_first, int ring) { return p < keep_first ? p : keep_first + (p - keep_first) % ring; }
+
+__global__ void k_attn_kv_store(const float * __restrict__ qkvg, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
+                                const int32_t * __restrict__ pos0, const int32_t * __restrict__ entry_of, AttnParams a, float * __restrict__ kcache,
+                                float * __restrict__ vcache, int64_t slot_stride) {
+    const int t = blockIdx.x;
+    const int e = entry_of[t];
+    const int n = off[e + 1] - off[e];
+    const int p = pos0[e] + (t - off[e]), pend = pos0[e] + n;
+    const int keep = min(a.keep_first, a.cache_rows), ring = a.cache_rows - keep;
+    // of the positions that share a ring row only the last one of this entry is stored
+    if (p >= keep && (ring <= 0 || p < pend - ring)) return;
+    const int row = cache_row(p, keep, max(ring, 1));
+    const int KD = a.kv_heads * a.dim, VD = a.kv_heads * a.vdim, C = attn_qkvg_cols(a);
+    const float * src = qkvg + (int64_t) t * C + a.heads * a.dim;
+    float * kd = kcache + (int64_t) slot[e] * slot_stride + (int64_t) row * KD;
+    float * vd = vcache + (int64_t) slot[e] * slot_stride + (int64_t) row * VD;
+    for (int i = threadIdx.x; i < KD; i += blockDim.x) kd[i] = src[i];
+    for (int i = threadIdx.x; i < VD; i += blockDim.x) vd[i] = src[KD + i];
+}
+
+// One warp owns one query row; a CTA of 4 warps shares key / value tiles of 32 positions in shared memory.
+// Lane j scores key j of the tile (fp32 dot over dim), the warp keeps a running max / sum (online softmax), then every lane
+// accumulates its share of the value dimensions.  NV = ceil(vdim / 32) accumulators per lane.
+constexpr int AQ = 4;      // queries per CTA (one per warp)
+constexpr int AKT = 32;    // keys per tile
+
+struct AttnAcc {
+    float m = -INFINITY, l = 0.f;
+};
+
+template <int NV>
+__device__ __forceinline__ void attn_tile_update(float score, bool valid, const float * __restrict__ vt, int vdim, int lane, float & m, float & l,
+                                                 float (&acc)[NV]) {
+    const float s = valid ? score : -INFINITY;
+    const float tmax = wmax(s);
+    if (tmax == -INFINITY) return;   // no visible key in this tile (uniform over the warp)
+    const float mn = fmaxf(m, tmax);
+    const float corr = m == -INFINITY ? 0.f : expf(m - mn);
+    const float p = valid ? expf(s - mn) : 0.f;
+    l = l * corr + wsum(p);
+#pragma unroll
+    for (int c = 0; c < NV; c++) acc[c] *= corr;
+    for (int j = 0; j < AKT; j++) {
+        const float pj = __shfl_sync(0xffffffffu, p, j);
+        if (pj != 0.f) {
+#pragma unroll
+            for (int c = 0; c < NV; c++) {
+                const int d = lane + 32 * c;
+                if (d < vdim) acc[c] = fmaf(pj, vt[j * vdim + d], acc[c]);
+            }
+        }
+    }
+    m = mn;
+}
+
+template <typename OT, int NV>
+__global__ void __launch_bounds__(AQ * 32) k_attn_window_prefill(const float * __restrict__ qkvg, const int32_t * __restrict__ off, AttnParams a,
+                                                                  OT * __restrict__ out) {
+    extern __shared__ float sm[];
+    const int e = blockIdx.z, h = blockIdx.y;
+    const int t_begin = off[e], n = off[e + 1] - t_begin;
+    const int q0 = blockIdx.x * AQ;
+    if (q0 >= n) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int D = a.dim, DV = a.vdim, C = attn_qkvg_cols(a);
+    const int kvh = h / (a.heads / a.kv_heads);
+    const int koff = a.heads * D + kvh * D, voff = a.heads * D + a.kv_heads * D + kvh * DV, goff = a.heads * D + a.kv_heads * D + a.kv_heads * DV + h;
+    float * qs = sm;                       // [AQ][D]
+    float * kt = qs + AQ * D;              // [AKT][D + 1]
+    float * vt = kt + AKT * (D + 1);       // [AKT][DV]
+    const int qi = q0 + warp;              // this warp's query position (entries handled here start at position 0)
+    const bool qok = qi < n;
+    for (int d = lane; d < D; d += 32) qs[warp * D + d] = qok ? qkvg[(int64_t) (t_begin + qi) * C + h * D + d] : 0.f;
+    const int q_last = min(q0 + AQ, n) - 1;
+    const bool windowed = a.window > 0;
+    const int w_lo = windowed ? max(0, q0 - a.window + 1) : 0;          // first key any query of the CTA sees through its window
+    const int s_hi = windowed ? min(a.keep_first, w_lo) : 0;            // kept first tokens below the window: [0, s_hi)
+    float m = -INFINITY, l = 0.f, acc[NV];
+#pragma unroll
+    for (int c = 0; c < NV; c++) acc[c] = 0.f;
+    // key ranges: the kept first tokens not covered by the window range, then the window range up to the last query
+    for (int range = 0; range < 2; range++) {
+        const int lo = range == 0 ? 0 : w_lo, hi = range == 0 ? s_hi : q_last + 1;
+        for (int k0 = lo; k0 < hi; k0 += AKT) {
+            __syncthreads();
+            const int nk = min(AKT, hi - k0);
+            for (int i = threadIdx.x; i < AKT * D; i += blockDim.x) {
+                const int j = i / D, d = i - j * D;
+                kt[j * (D + 1) + d] = j < nk ? qkvg[(int64_t) (t_begin + k0 + j) * C + koff + d] : 0.f;
+            }
+            for (int i = threadIdx.x; i < AKT * DV; i += blockDim.x) {
+                const int j = i / DV, d = i - j * DV;
+                vt[i] = j < nk ? qkvg[(int64_t) (t_begin + k0 + j) * C + voff + d] : 0.f;
+            }
+            __syncthreads();
+            if (!qok) continue;
+            const int kj = k0 + lane;
+            bool valid = lane < nk && kj <= qi && (!windowed || qi - kj < a.window || kj < a.keep_first);
+            float s = 0.f;
+            const float * qr = qs + warp * D, * kr = kt + lane * (D + 1);
+            for (int d = 0; d < D; d++) s = fmaf(qr[d], kr[d], s);
+            s *= a.scale;
+            if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+            attn_tile_update<NV>(s, valid, vt, DV, lane, m, l, acc);
+        }
+    }
+    if (!qok) return;
+    const float gate = sigmoid_f(qkvg[(int64_t) (t_begin + qi) * C + goff]);
+    const float inv = l > 0.f ? gate / l : 0.f;
+#pragma unroll
+    for (int c = 0; c < NV; c++) {
+        const int d = lane + 32 * c;
+        if (d < DV) put(out, (int64_t) (t_begin + qi) * (a.heads * DV) + h * DV + d, acc[c] * inv);
+    }
+}
+
+// decode: one CTA of 4 warps per (head, entry); warp w takes cache rows w*32, w*32+128, ...; partial softmax states merged in shared memory
+template <typename OT, int NV>
+__global__ void __launch_bounds__(128) k_attn_window_decode(const float * __restrict__ qkvg, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
+                                                            const int32_t * __restrict__ pos0, AttnParams a, const float * __restrict__ kcache,
+                                                            const float * __restrict__ vcache, int64_t slot_stride, OT * __restrict__ out) {
+    extern __shared__ float sm[];
+    const int e = blockIdx.y, h = blockIdx.x;
+    const int t = off[e];
+    const int pi = pos0[e];               // position of the query (its own K / V row is in the cache already)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int D = a.dim, DV = a.vdim, C = attn_qkvg_cols(a);
+    const int kvh = h / (a.heads / a.kv_heads);
+    const int KD = a.kv_heads * D, VD = a.kv_heads * DV;
+    const int keep = min(a.keep_first, a.cache_rows), ring = a.cache_rows - keep;
+    float * qs = sm;                       // [D]
+    float * mm = qs + D;                   // [4] max, [4] sum
+    float * accs = mm + 8;                 // [4][NV*32]
+    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = qkvg[(int64_t) t * C + h * D + d];
+    __syncthreads();
+    const float * kc = kcache + (int64_t) slot[e] * slot_stride, * vc = vcache + (int64_t) slot[e] * slot_stride;
+    float m = -INFINITY, l = 0.f, acc[NV];
+#pragma unroll
+    for (int c = 0; c < NV; c++) acc[c] = 0.f;
+    const int rows_used = min(a.cache_rows, pi + 1);
+    for (int r0 = warp * 32; r0 < rows_used; r0 += 128) {
+        const int r = r0 + lane;
+        // which position does row r hold right now?
+        int p = -1;
+        if (r < rows_used) {
+            if (r < keep) p = r;
+            else {
+                const int rr = r - keep, ip = pi - keep;       // ip >= 0 here because r < rows_used <= pi + 1
+                p = keep + ip - ((ip - rr) % ring + ring) % ring;
+                if (p < keep) p = -1;
+            }
+        }
+        const bool valid = p >= 0 && p <= pi && (a.window <= 0 || pi - p < a.window || p < a.keep_first);
+        float s = 0.f;
+        if (valid) {
+            const float * kr = kc + (int64_t) r * KD + kvh * D;
+            for (int d = 0; d < D; d++) s = fmaf(qs[d], kr[d], s);
+            s *= a.scale;
+            if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+        }
+        const float sv = valid ? s : -INFINITY;
+        const float tmax = wmax(sv);
+        if (tmax == -INFINITY) continue;
+        const float mn = fmaxf(m, tmax);
+        const float corr = m == -INFINITY ? 0.f : expf(m - mn);
+        const float p_ = valid ? expf(sv - mn) : 0.f;
+        l = l * corr + wsum(p_);
+#pragma unroll
+        for (int c = 0; c < NV; c++) acc[c] *= corr;
+        for (int j = 0; j < 32; j++) {
+            const float pj = __shfl_sync(0xffffffffu, p_, j);
+            if (pj != 0.f) {
+                const float * vr = vc + (int64_t) (r0 + j) * VD + kvh * DV;
+#pragma unroll
+                for (int c = 0; c < NV; c++) {
+                    const int d = lane + 32 * c;
+                    if (d < DV) acc[c] = fmaf(pj, vr[d], acc[c]);
+                }
+            }
+        }
+        m = mn;
+    }
+    if (lane == 0) { mm[warp] = m; mm[4 + warp] = l; }
+#pragma unroll
+    for (int c = 0; c < NV; c++) accs[warp * NV * 32 + c * 32 + lane] = acc[c];
+    __syncthreads();
+    if (warp == 0) {
+        float M = fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3]));
+        float L = 0.f, o[NV];
+#pragma unroll
+        for (int c = 0; c < NV; c++) o[c] = 0.f;
+        for (int w = 0; w < 4; w++) {
+            if (mm[w] == -INFINITY) continue;
+            const float f = expf(mm[w] - M);
+            L += mm[4 + w] * f;
+#pragma unroll
+            for (int c = 0; c < NV; c++) o[c] = fmaf(accs[w * NV * 32 + c * 32 + lane], f, o[c]);
+        }
+        const float gate = sigmoid_f(qkvg[(int64_t) t * C + a.heads * D + KD + VD + h]);
+        const float inv = L > 0.f ? gate / L : 0.f;
+#pragma unroll
+        for (int c = 0; c < NV; c++) {
+            const int d = lane + 32 * c;
+            if (d < DV) put(out, (int64_t) t * (a.heads * DV) + h * DV + d, o[c] * inv);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Mamba-2
+__global__ void k_mamba2_conv(const float * __restrict__ u, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
+                              const int32_t * __restrict__ entry_of, Mamba2Params p, const float * __restrict__ w, const float * __restrict__ bias,
+                              const float * __restrict__ conv_state, int64_t slot_stride, float * __restrict__ xbc) {
+    const int t = blockIdx.x;
+    const int e = entry_of[t];
+    const int lt = t - off[e];
+    const int CH = mamba2_conv_channels(p), U = mamba2_in_cols(p), inner = mamba2_inner(p), taps = p.conv;
+    const float * st = conv_state + (int64_t) slot[e] * slot_stride;   // [taps-1][CH], row taps-2 = the input just before this entry
+    for (int c = threadIdx.x; c < CH; c += blockDim.x) {
+        float acc = bias[c];
+        for (int d = 0; d < taps; d++) {
+            const int l2 = lt - d;
+            const float in = l2 >= 0 ? u[(int64_t) (t - d) * U + inner + c] : st[(int64_t) (taps - 1 + l2) * CH + c];
+            acc = fmaf(w[(int64_t) c * taps + (taps - 1 - d)], in, acc);
+        }
+        xbc[(int64_t) t * CH + c] = silu_f(acc);
+    }
+}
+__global__ void k_mamba2_conv_state(const float * __restrict__ u, const int32_t * __restrict__ slot, const int32_t * __restrict__ off, Mamba2Params p,
+                                    float * __restrict__ conv_state, int64_t slot_stride) {
+    const int e = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int CH = mamba2_conv_channels(p), U = mamba2_in_cols(p), inner = mamba2_inner(p), taps = p.conv;
+    if (c >= CH) return;
+    const int n = off[e + 1] - off[e];
+    float * st = conv_state + (int64_t) slot[e] * slot_stride;
+    for (int k = 0; k < taps - 1; k++) {     // ascending: row k + n is read before a later iteration overwrites it
+        const int l2 = n - (taps - 1) + k;   // index within the entry of the input that becomes state row k
+        st[(int64_t) k * CH + c] = l2 >= 0 ? u[(int64_t) (off[e] + l2) * U + inner + c] : st[(int64_t) (k + n) * CH + c];
+    }
+}
+
+// one CTA per (head, entry); the state S [N][P] lives in shared memory for the whole entry, tokens are walked in order
+__global__ void __launch_bounds__(256) k_mamba2_scan(const float * __restrict__ u, const float * __restrict__ xbc, const int32_t * __restrict__ slot,
+                                                     const int32_t * __restrict__ off, Mamba2Params p, const float * __restrict__ dt_bias,
+                                                     const float * __restrict__ A_log, const float * __restrict__ Dp, float * __restrict__ ssm_state,
+                                                     int64_t slot_stride, float * __restrict__ y) {
+    extern __shared__ float sm[];
+    const int h = blockIdx.x, e = blockIdx.y;
+    const int N = p.state, P = p.vdim, inner = mamba2_inner(p), CH = mamba2_conv_channels(p), U = mamba2_in_cols(p);
+    const int g = h / (p.heads / p.groups);
+    float * S = sm;               // [N][P]
+    float * Bs = S + N * P;       // [N]
+    float * Cs = Bs + N;          // [N]
+    float * xs = Cs + N;          // [P]
+    float * gst = ssm_state + (int64_t) slot[e] * slot_stride + (int64_t) h * N * P;
+    for (int i = threadIdx.x; i < N * P; i += blockDim.x) S[i] = gst[i];
+    const float A = -expf(A_log[h]), dtb = dt_bias[h], Dh = Dp[h];
+    const int t0 = off[e], n = off[e + 1] - t0;
+    for (int lt = 0; lt < n; lt++) {
+        const int t = t0 + lt;
+        __syncthreads();
+        for (int i = threadIdx.x; i < N; i += blockDim.x) {
+            Bs[i] = xbc[(int64_t) t * CH + inner + g * N + i];
+            Cs[i] = xbc[(int64_t) t * CH + inner + p.groups * N + g * N + i];
+        }
+        for (int i = threadIdx.x; i < P; i += blockDim.x) xs[i] = xbc[(int64_t) t * CH + h * P + i];
+        const float raw = u[(int64_t) t * U + 2 * inner + 2 * p.groups * N + h] + dtb;
+        const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+        const float decay = expf(A * dt);
+        __syncthreads();
+        for (int i = threadIdx.x; i < N * P; i += blockDim.x) {
+            const int nn = i / P, pp = i - nn * P;
+            S[i] = fmaf(decay, S[i], dt * Bs[nn] * xs[pp]);
+        }
+        __syncthreads();
+        for (int pp = threadIdx.x; pp < P; pp += blockDim.x) {
+            float acc = 0.f;
+            for (int nn = 0; nn < N; nn++) acc = fmaf(S[nn * P + pp], Cs[nn], acc);
+            y[(int64_t) t * inner + h * P + pp] = acc + Dh * xs[pp];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < N * P; i += blockDim.x) gst[i] = S[i];
+}
+
+template <typename OT>
+__global__ void __launch_bounds__(256) k_mamba2_gate_norm(const float * __restrict__ y, const float * __restrict__ u, Mamba2Params p, const float * __restrict__ w,
+                                                          float eps, OT * __restrict__ out) {
+    __shared__ float red[33];
+    const int t = blockIdx.x, grp = blockIdx.y;
+    const int inner = mamba2_inner(p), U = mamba2_in_cols(p), part = inner / p.norm_groups;
+    const float * yr = y + (int64_t) t * inner + grp * part, * zr = u + (int64_t) t * U + grp * part;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) { const float v = yr[i] * silu_f(zr[i]); q = fmaf(v, v, q); }
+    const float inv = 1.f / sqrtf(block_sum(q, red) / (float) part + eps);
+    for (int i = threadIdx.x; i < part; i += blockDim.x)
+        put(out, (int64_t) t * inner + grp * part + i, yr[i] * silu_f(zr[i]) * inv * w[grp * part + i]);
+}
+
+template <typename F> int ck_launch(F && f) {
+    g_launches++;
+    f();
+    return (int) cudaGetLastError();
+}
+template <typename K> int raise_smem(K kernel, size_t bytes) {
+    if (bytes <= 48 * 1024) return 0;
+    return (int) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) bytes);
+}
+
+}  // namespace
+
+int launch_embed(const void * table, int type, int width, const int32_t * tokens, int n_tokens, float * x, float * x_copy, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    return ck_launch([&] {
+        if (type == T_BF16) k_embed<__nv_bfloat16><<<n_tokens, 128, 0, st>>>((const __nv_bfloat16 *) table, width, tokens, x, x_copy);
+        else k_embed<float><<<n_tokens, 128, 0, st>>>((const float *) table, width, tokens, x, x_copy);
+    });
+}
+int launch_cast(const float * x, void * y, int otype, int64_t n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned) ((n + 255) / 256);
+    return ck_launch([&] {
+        if (otype == T_BF16) k_cast<__nv_bfloat16><<<grid, 256, 0, st>>>(x, (__nv_bfloat16 *) y, n);
+        else k_cast<float><<<grid, 256, 0, st>>>(x, (float *) y, n);
+    });
+}
+int launch_layernorm(const float * x, const int32_t * rows, const float * w, float eps, void * y, int otype, int n_rows, int width, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    return ck_launch([&] {
+        if (otype == T_BF16) k_layernorm<__nv_bfloat16, false><<<n_rows, 256, 0, st>>>(x, rows, w, eps, (__nv_bfloat16 *) y, nullptr, width);
+        else k_layernorm<float, false><<<n_rows, 256, 0, st>>>(x, rows, w, eps, (float *) y, nullptr, width);
+    });
+}
+int launch_layernorm_residual(const float * m, const float * w, float eps, float * x, int n_rows, int width, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    return ck_launch([&] { k_layernorm<float, true><<<n_rows, 256, 0, st>>>(m, nullptr, w, eps, nullptr, x, width); });
+}
+int launch_gelu_mul(const float * gu, void * y, int otype, int n_tokens, int ff, cudaStream_t st) {
+    const int64_t n = (int64_t) n_tokens * ff;
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned) ((n + 255) / 256);
+    return ck_launch([&] {
+        if (otype == T_BF16) k_gelu_mul<__nv_bfloat16><<<grid, 256, 0, st>>>(gu, (__nv_bfloat16 *) y, n_tokens, ff);
+        else k_gelu_mul<float><<<grid, 256, 0, st>>>(gu, (float *) y, n_tokens, ff);
+    });
+}
+int launch_argmax_rows(const float * logits, int n, int n_rows, int32_t * out, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    return ck_launch([&] { k_argmax_rows<<<n_rows, 256, 0, st>>>(logits, n, out); });
+}
+
+int launch_attn_kv_store(const float * qkvg, const BatchView & b, const AttnParams & a, float * kcache, float * vcache, int64_t slot_stride, cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    return ck_launch([&] { k_attn_kv_store<<<b.n_tokens, 128, 0, st>>>(qkvg, b.slot, b.off, b.pos0, b.entry_of, a, kcache, vcache, slot_stride); });
+}
+
+#define PB_NV_DISPATCH(NVV, CALL)                                  \
+    do {                                                           \
+        if ((NVV) <= 1) { constexpr int NV = 1; CALL; }            \
+        else if ((NVV) <= 2) { constexpr int NV = 2; CALL; }       \
+        else if ((NVV) <= 4) { constexpr int NV = 4; CALL; }       \
+        else if ((NVV) <= 8) { constexpr int NV = 8; CALL; }       \
+        else return (int) cudaErrorInvalidValue;                   \
+    } while (0)
+
+template <typename OT, int NV>
+static int attn_prefill_typed(const float * qkvg, const BatchView & b, const AttnParams & a, OT * out, cudaStream_t st) {
+    const size_t smem = ((size_t) AQ * a.dim + (size_t) AKT * (a.dim + 1) + (size_t) AKT * a.vdim) * sizeof(float);
+    int rc = raise_smem(k_attn_window_prefill<OT, NV>, smem);
+    if (rc) return rc;
+    const dim3 grid((unsigned) ((b.max_n + AQ - 1) / AQ), (unsigned) a.heads, (unsigned) b.n_entries);
+    return ck_launch([&] { k_attn_window_prefill<OT, NV><<<grid, AQ * 32, smem, st>>>(qkvg, b.off, a, out); });
+}
+int launch_attn_window_prefill(const float * qkvg, const BatchView & b, const AttnParams & a, void * out, int otype, cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads != 0 || a.dim <= 0 || a.vdim <= 0) return (int) cudaErrorInvalidValue;
+    const int nv = (a.vdim + 31) / 32;
+    if (otype == T_BF16) PB_NV_DISPATCH(nv, return (attn_prefill_typed<__nv_bfloat16, NV>(qkvg, b, a, (__nv_bfloat16 *) out, st)));
+    else PB_NV_DISPATCH(nv, return (attn_prefill_typed<float, NV>(qkvg, b, a, (float *) out, st)));
+    return 0;
+}
+template <typename OT, int NV>
+static int attn_decode_typed(const float * qkvg, const BatchView & b, const AttnParams & a, const float * kc, const float * vc, int64_t stride, OT * out,
+                             cudaStream_t st) {
+    const size_t smem = ((size_t) a.dim + 8 + 4 * NV * 32) * sizeof(float);
+    int rc = raise_smem(k_attn_window_decode<OT, NV>, smem);
+    if (rc) return rc;
+    const dim3 grid((unsigned) a.heads, (unsigned) b.n_entries);
+    return ck_launch([&] { k_attn_window_decode<OT, NV><<<grid, 128, smem, st>>>(qkvg, b.slot, b.off, b.pos0, a, kc, vc, stride, out); });
+}
+int launch_attn_window_decode(const float * qkvg, const BatchView & b, const AttnParams & a, const float * kcache, const float * vcache, int64_t slot_stride,
+                              void * out, int otype, cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads != 0 || a.dim <= 0 || a.vdim <= 0) return (int) cudaErrorInvalidValue;
+    const int nv = (a.vdim + 31) / 32;
+    if (otype == T_BF16) PB_NV_DISPATCH(nv, return (attn_decode_typed<__nv_bfloat16, NV>(qkvg, b, a, kcache, vcache, slot_stride, (__nv_bfloat16 *) out, st)));
+    else PB_NV_DISPATCH(nv, return (attn_decode_typed<float, NV>(qkvg, b, a, kcache, vcache, slot_stride, (float *) out, st)));
+    return 0;
+}
+
+int launch_mamba2_conv(const float * u, const BatchView & b, const Mamba2Params & p, const float * w, const float * bias, float * conv_state,
+                       int64_t slot_stride, float * xbc, cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    if (p.conv < 1) return (int) cudaErrorInvalidValue;
+    int rc = ck_launch([&] { k_mamba2_conv<<<b.n_tokens, 256, 0, st>>>(u, b.slot, b.off, b.entry_of, p, w, bias, conv_state, slot_stride, xbc); });
+    if (rc || p.conv < 2) return rc;
+    const dim3 grid((unsigned) ((mamba2_conv_channels(p) + 127) / 128), (unsigned) b.n_entries);
+    return ck_launch([&] { k_mamba2_conv_state<<<grid, 128, 0, st>>>(u, b.slot, b.off, p, conv_state, slot_stride); });
+}
+int launch_mamba2_scan(const float * u, const float * xbc, const BatchView & b, const Mamba2Params & p, const float * dt_bias, const float * A_log,
+                       const float * D, float * ssm_state, int64_t slot_stride, float * y, cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    if (p.heads <= 0 || p.groups <= 0 || p.heads % p.groups != 0) return (int) cudaErrorInvalidValue;
+    const size_t smem = ((size_t) p.state * p.vdim + 2 * (size_t) p.state + p.vdim) * sizeof(float);
+    int rc = raise_smem(k_mamba2_scan, smem);
+    if (rc) return rc;
+    const dim3 grid((unsigned) p.heads, (unsigned) b.n_entries);
+    return ck_launch([&] { k_mamba2_scan<<<grid, 256, smem, st>>>(u, xbc, b.slot, b.off, p, dt_bias, A_log, D, ssm_state, slot_stride, y); });
+}
+int launch_mamba2_gate_norm(const float * y, const float * u, const Mamba2Params & p, const float * w, float eps, void * out, int otype, int n_tokens,
+                            cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (p.norm_groups <= 0 || mamba2_inner(p) % p.norm_groups != 0) return (int) cudaErrorInvalidValue;
+    const dim3 grid((unsigned) n_tokens, (unsigned) p.norm_groups);
+    return ck_launch([&] {
+        if (otype == T_BF16) k_mamba2_gate_norm<__nv_bfloat16><<<grid, 256, 0, st>>>(y, u, p, w, eps, (__nv_bfloat16 *) out);
+        else k_mamba2_gate_norm<float><<<grid, 256, 0, st>>>(y, u, p, w, eps, (float *) out);
+    });
+}
+
+}  // namespace pb

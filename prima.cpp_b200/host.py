@@ -8,7 +8,8 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
 
-TYPES = {"f32": 0, "f16": 1, "q5_1": 7, "q8_0": 8, "q4_K": 12, "q5_K": 13, "q6_K": 14}
+TYPES = {"f32": 0, "f16": 1, "q5_1": 7, "q8_0": 8, "q4_K": 12, "q5_K": 13, "q6_K": 14, "bf16": 30}
+COMPUTE_TYPES = {"bfloat16": 30, "bf16": 30, "float32": 0, "f32": 0}
 
 
 def lib_path() -> Path:
@@ -21,7 +22,8 @@ def build(force: bool = False) -> Path:
     """Compile libprima_b200.so for sm_100a with nvcc (cross-compiles without a GPU)."""
     if force:
         subprocess.check_call(["make", "-C", str(PKG / "csrc"), "clean"], stdout=subprocess.DEVNULL)
-    subprocess.check_call(["make", "-C", str(PKG / "csrc"), "-j4"], stdout=subprocess.DEVNULL)
+    import os
+    subprocess.check_call(["make", "-C", str(PKG / "csrc"), f"-j{max(2, min(16, os.cpu_count() or 4))}"], stdout=subprocess.DEVNULL)
     return lib_path()
 
 
@@ -29,6 +31,10 @@ class HParams(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n_vocab", "n_ctx",
                                           "rope_mode", "n_ctx_orig")] + \
                [(n, C.c_float) for n in ("rope_freq_base", "rope_freq_scale", "rms_eps")]
+
+
+class BatchEntry(C.Structure):
+    _fields_ = [("seq", C.c_int32), ("n_tokens", C.c_int32), ("tokens", C.POINTER(C.c_int32)), ("n_want", C.c_int32), ("want", C.POINTER(C.c_int32))]
 
 
 class Pb200Error(RuntimeError):
@@ -107,6 +113,19 @@ class Lib:
         for n in ("pb200_token_device", "pb200_sample_device"):
             getattr(c, n).restype = vp
             getattr(c, n).argtypes = [vp, C.c_int]
+        c.pb200_arch_name.restype = C.c_char_p
+        c.pb200_arch_name.argtypes = [C.c_int]
+        c.pb200_arch_family.argtypes = [C.c_char_p]
+        c.pb200_model_create_from_config.restype = vp
+        c.pb200_model_create_from_config.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int]
+        c.pb200_model_load_dir.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(vp)]
+        c.pb200_model_get_hparams.argtypes = [vp, C.POINTER(HParams)]
+        c.pb200_model_n_seq.argtypes = [vp]
+        c.pb200_seq_alloc.argtypes = [vp]
+        c.pb200_seq_free.argtypes = [vp, C.c_int]
+        c.pb200_seq_length.argtypes = [vp, C.c_int]
+        c.pb200_batch_step.argtypes = [vp, C.c_int, C.POINTER(BatchEntry), vp, vp]
+        c.pb200_debug_tap_layers.argtypes = [vp, C.c_int]
 
     @classmethod
     def get(cls) -> "Lib":
@@ -149,6 +168,78 @@ class Model:
         m.h = h.value
         m.load_seconds, m.load_bytes = secs.value, nbytes.value
         return m
+
+    @classmethod
+    def _wrap(cls, lib, handle) -> "Model":
+        m = cls.__new__(cls)
+        m.lib = lib
+        m.h = handle
+        m.hp = HParams()
+        lib.check(lib.c.pb200_model_get_hparams(handle, C.byref(m.hp)), "model_get_hparams")
+        return m
+
+    @classmethod
+    def from_config(cls, config, dtype: str = "bfloat16", device: int = 0, n_ctx: int = 4096, n_seq: int = 0) -> "Model":
+        """A model of the layer-list family from its configuration (dict or JSON text); tensors follow through set_tensor, then finalize."""
+        import json
+        lib = Lib.get()
+        text = config if isinstance(config, str) else json.dumps(config)
+        h = lib.c.pb200_model_create_from_config(text.encode(), COMPUTE_TYPES[dtype], device, int(n_ctx), int(n_seq))
+        if not h:
+            raise Pb200Error("pb200_model_create_from_config failed (unknown architecture, bad configuration or no CUDA device)")
+        return cls._wrap(lib, h)
+
+    @classmethod
+    def from_dir(cls, path, dtype: str = "bfloat16", device: int = 0, n_ctx: int = 4096, n_seq: int = 0) -> "Model":
+        """config.json + model.safetensors of a directory -> finalized model (pb200_model_load_dir)."""
+        lib = Lib.get()
+        h = C.c_void_p()
+        lib.check(lib.c.pb200_model_load_dir(str(path).encode(), COMPUTE_TYPES[dtype], device, int(n_ctx), int(n_seq), C.byref(h)), "model_load_dir")
+        return cls._wrap(lib, h.value)
+
+    # ---- sequence slots and the ragged batch step (layer-list family) ----
+    @property
+    def n_seq(self) -> int:
+        return self.lib.c.pb200_model_n_seq(self.h)
+
+    def seq_alloc(self) -> int:
+        s = self.lib.c.pb200_seq_alloc(self.h)
+        if s < 0:
+            self.lib.check(s, "seq_alloc")
+        return s
+
+    def seq_free(self, slot: int) -> None:
+        self.lib.check(self.lib.c.pb200_seq_free(self.h, slot), "seq_free")
+
+    def seq_length(self, slot: int) -> int:
+        return self.lib.c.pb200_seq_length(self.h, slot)
+
+    def batch_step(self, entries, greedy: bool = False):
+        """entries: [(slot, tokens, want)] with want = indices into tokens whose logits are asked for.  Returns (logits [rows, n_vocab]
+        float32 in the order of the entries and of want, greedy tokens per entry or None)."""
+        import numpy as np
+        n = len(entries)
+        arr = (BatchEntry * n)()
+        keep = []
+        rows = 0
+        for i, (slot, tokens, want) in enumerate(entries):
+            t = np.ascontiguousarray(tokens, dtype=np.int32)
+            w = np.ascontiguousarray(want, dtype=np.int32)
+            keep += [t, w]
+            arr[i].seq = int(slot)
+            arr[i].n_tokens = int(t.size)
+            arr[i].tokens = t.ctypes.data_as(C.POINTER(C.c_int32))
+            arr[i].n_want = int(w.size)
+            arr[i].want = w.ctypes.data_as(C.POINTER(C.c_int32)) if w.size else None
+            rows += int(w.size)
+        logits = np.empty((rows, self.hp.n_vocab), dtype=np.float32)
+        g = np.zeros(n, dtype=np.int32) if greedy else None
+        self.lib.check(self.lib.c.pb200_batch_step(self.h, n, arr, logits.ctypes.data_as(C.c_void_p) if rows else None,
+                                                   g.ctypes.data_as(C.c_void_p) if greedy else None), "batch_step")
+        return logits, (g.tolist() if greedy else None)
+
+    def tap_layers(self, on: bool = True) -> None:
+        self.lib.check(self.lib.c.pb200_debug_tap_layers(self.h, int(on)), "debug_tap_layers")
 
     def set_tensor(self, name: str, ttype: int, data) -> None:
         import numpy as np
