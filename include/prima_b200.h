@@ -237,6 +237,12 @@ PB200_API int pb200_set_hidden(pb200_model * m, const float * hidden_host);   /*
 PB200_API int pb200_debug_read(pb200_model * m, const char * name, float * host, int64_t n);   /* white-box tests: q,k,v,att,g,u,x_a,x_b,xn,logits */
 PB200_API int pb200_set_use_graph(pb200_model * m, int on);             /* CUDA-graph replay on/off (default on) */
 
+/* dense product, device buffers: C[t][n] = alpha * sum_k A[t][k] W[n][k] (+ bias[n]) (+ resid[t][n]); A [T][K] and W [N][K] row-major of `type`
+ * (PB200_TYPE_F32: true fp32; PB200_TYPE_BF16: bf16 operands, fp32 accumulation: tcgen05 tensor cores for more than 8 tokens when K and
+ * the strides are multiples of 8, a weight-streaming kernel for up to 8 tokens); C, bias, resid f32; resid may alias C; strides in elements */
+PB200_API int pb200_dense(int type, const void * A, int64_t lda, const void * W, int64_t ldw, float * C, int64_t ldc, int T, int N, int K,
+                          const float * bias, const float * resid, int64_t ldr, float alpha, void * stream);
+
 /* ---- architectures ----
  * Two families share the model object: 0 = one fixed transformer graph over k-quant GGUF weights ("llama", "qwen2":
  * pb200_model_create / pb200_model_load_gguf), 1 = layer list: a configuration file lists the layers, each with a sequence mixer
@@ -282,6 +288,10 @@ PB200_API int pb200_batch_step(pb200_model * m, int n_entries, const pb200_batch
 /* white-box tests: on != 0 keeps the residual stream after every layer run of the next batches; read it with
  * pb200_debug_read(m, "layers", host, runs * tokens * n_embd) */
 PB200_API int pb200_debug_tap_layers(pb200_model * m, int on);
+/* measurement: on != 0 records CUDA events around every launch of the next batches; pb200_debug_read(m, "profile", host, 8) returns the
+ * device milliseconds of the last batch per category: dense products, attention, convolution, scan, norms, element-wise, output head,
+ * [7] total.  Events serialise nothing but forbid overlap between launches; leave it off when timing whole steps. */
+PB200_API int pb200_debug_profile(pb200_model * m, int on);
 
 #ifdef __cplusplus
 }

@@ -114,6 +114,11 @@ struct LayerList {
     int64_t tap_floats = 0, tap_cap = 0;
     int tap_T = 0;
     int64_t weight_bytes = 0;
+    // per-category device time of the last batch step (bench): CUDA events around every launch while prof_on
+    bool prof_on = false;
+    std::vector<cudaEvent_t> prof_ev;
+    std::vector<int> prof_cat;
+    float prof_ms[8] = {0};
     std::vector<int> rows_tmp;      // logits row of the caller (or -(entry+1) for a greedy row) per wanted row of the last sub-batch
 };
 
@@ -457,6 +462,7 @@ void ll_free(pb200_model * m) {
     if (ll->greedy_host) cudaFreeHost(ll->greedy_host);
     if (ll->logits_host) cudaFreeHost(ll->logits_host);
     if (ll->tap) cudaFree(ll->tap);
+    for (cudaEvent_t e : ll->prof_ev) cudaEventDestroy(e);
     delete ll;
     m->ll = nullptr;
 }
@@ -557,9 +563,22 @@ static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
 // One homogeneous ragged batch through every layer run.  `prefill`: every entry starts at position 0 (keys and values are read from
 // the batch); otherwise every entry brings one token (keys and values come from the slot's cache).  Rows `want_dev[0..nW)` (token
 // indices of the batch) go through the final norm and the output head into logits rows lrow0 ...
+enum : int { CAT_DENSE = 0, CAT_ATTN = 1, CAT_CONV = 2, CAT_SCAN = 3, CAT_NORM = 4, CAT_ELEM = 5, CAT_HEAD = 6, N_CAT = 7 };
+static int prof_mark(pb200_model * m, int cat) {   // an event before the launch of a category; the next mark (or the end) closes its interval
+    LayerList & ll = *m->ll;
+    if (!ll.prof_on) return 0;
+    const size_t i = ll.prof_cat.size();
+    if (ll.prof_ev.size() <= i) { cudaEvent_t e; CK(cudaEventCreate(&e)); ll.prof_ev.push_back(e); }
+    ll.prof_cat.push_back(cat);
+    return (int) cudaEventRecord(ll.prof_ev[i], m->stream);
+}
+#define CAT(c) CK(prof_mark(m, c))
+
 static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const int32_t * tokens_dev, const int32_t * want_dev, int nW, int lrow0) {
     LayerList & ll = *m->ll;
     cudaStream_t st = m->stream;
+    ll.prof_cat.clear();
+    CAT(CAT_ELEM);
     const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
     CK(launch_embed(ll.embed.data, ct, W, tokens_dev, T, ll.x, ll.x0, st));
     float * x = ll.x, * xalt = ll.xalt;
@@ -580,47 +599,78 @@ static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const 
         LLayer & L = ll.layers[(size_t) r.layer];
         if (r.pass >= 0) {
             // x <- W_in [x ; x0] + step[pass]: two products over the halves of W_in, the second accumulating onto the first
+            CAT(CAT_ELEM);
             CK(launch_cast(x, ll.act, ct, (int64_t) T * W, st));
             CK(launch_cast(ll.x0, ll.act2, ct, (int64_t) T * W, st));
+            CAT(CAT_DENSE);
             CK(launch_dense(ct, ll.act, W, ll.loop_in.data, 2 * W, xalt, W, T, W, W, ll.loop_step.data + (int64_t) r.pass * W, nullptr, 0, 1.f, st));
             CK(launch_dense(ct, ll.act2, W, (const uint8_t *) ll.loop_in.data + (size_t) W * esize(ct), 2 * W, xalt, W, T, W, W, nullptr, xalt, W, 1.f, st));
             std::swap(x, xalt);
         }
         float * sbase = ll.state + r.state_off;
+        CAT(CAT_NORM);
         CK(launch_layernorm(x, nullptr, L.norm1.data, ll.eps, ll.act, ct, T, W, st));
         if (L.kind == MIX_ATTENTION) {
             const AttnParams & a = L.att;
             const int C = attn_qkvg_cols(a);
+            CAT(CAT_DENSE);
             CK(launch_dense(ct, ll.act, W, L.qkvg.data, W, ll.big, C, T, C, W, nullptr, nullptr, 0, 1.f, st));
             float * kc = sbase, * vc = sbase + (int64_t) a.cache_rows * a.kv_heads * a.dim;
+            CAT(CAT_ATTN);
             CK(launch_attn_kv_store(ll.big, b, a, kc, vc, ll.slot_floats, st));
             if (prefill) CK(launch_attn_window_prefill(ll.big, b, a, ll.act, ct, st));
             else CK(launch_attn_window_decode(ll.big, b, a, kc, vc, ll.slot_floats, ll.act, ct, st));
+            CAT(CAT_DENSE);
             CK(launch_dense(ct, ll.act, (int64_t) a.heads * a.vdim, L.out.data, (int64_t) a.heads * a.vdim, ll.msub, W, T, W, a.heads * a.vdim, nullptr, nullptr, 0,
                             1.f, st));
         } else {
             const Mamba2Params & p = L.ssm;
             const int U = mamba2_in_cols(p), inner = mamba2_inner(p);
+            CAT(CAT_DENSE);
             CK(launch_dense(ct, ll.act, W, L.in.data, W, ll.big, U, T, U, W, nullptr, nullptr, 0, 1.f, st));
             float * cs = sbase, * ss = sbase + (int64_t) (p.conv - 1) * mamba2_conv_channels(p);
+            CAT(CAT_CONV);
             CK(launch_mamba2_conv(ll.big, b, p, L.conv_w.data, L.conv_b.data, cs, ll.slot_floats, ll.xbc, st));
+            CAT(CAT_SCAN);
             CK(launch_mamba2_scan(ll.big, ll.xbc, b, p, L.dt_bias.data, L.A_log.data, L.D.data, ss, ll.slot_floats, ll.yssm, st));
+            CAT(CAT_NORM);
             CK(launch_mamba2_gate_norm(ll.yssm, ll.big, p, L.gnorm.data, ll.eps, ll.act, ct, T, st));
+            CAT(CAT_DENSE);
             CK(launch_dense(ct, ll.act, inner, L.out.data, inner, ll.msub, W, T, W, inner, nullptr, nullptr, 0, 1.f, st));
         }
+        CAT(CAT_NORM);
         CK(launch_layernorm_residual(ll.msub, L.norm1b.data, ll.eps, x, T, W, st));
         if (L.ff > 0) {
+            CAT(CAT_NORM);
             CK(launch_layernorm(x, nullptr, L.norm2.data, ll.eps, ll.act, ct, T, W, st));
+            CAT(CAT_DENSE);
             CK(launch_dense(ct, ll.act, W, L.gateup.data, W, ll.big, 2 * L.ff, T, 2 * L.ff, W, nullptr, nullptr, 0, 1.f, st));
+            CAT(CAT_ELEM);
             CK(launch_gelu_mul(ll.big, ll.act, ct, T, L.ff, st));
+            CAT(CAT_DENSE);
             CK(launch_dense(ct, ll.act, L.ff, L.down.data, L.ff, ll.msub, W, T, W, L.ff, nullptr, nullptr, 0, 1.f, st));
+            CAT(CAT_NORM);
             CK(launch_layernorm_residual(ll.msub, L.norm2b.data, ll.eps, x, T, W, st));
         }
         if (ll.tap_on) CK(cudaMemcpyAsync(ll.tap + (int64_t) ir * T * W, x, (size_t) T * W * 4, cudaMemcpyDeviceToDevice, st));
     }
     if (nW > 0) {
+        CAT(CAT_HEAD);
         CK(launch_layernorm(x, want_dev, ll.final_norm.data, ll.eps, ll.actw, ct, nW, W, st));
         CK(launch_dense(ct, ll.actw, W, ll.head.data, W, ll.logits + (int64_t) lrow0 * ll.vocab, ll.vocab, nW, ll.vocab, W, nullptr, nullptr, 0, ll.logit_scale, st));
+    }
+    CAT(-1);
+    return 0;
+}
+static int prof_collect(pb200_model * m) {   // after the stream has been synchronised
+    LayerList & ll = *m->ll;
+    if (!ll.prof_on) return 0;
+    for (int c = 0; c < 8; c++) ll.prof_ms[c] = 0.f;
+    for (size_t i = 0; i + 1 < ll.prof_cat.size(); i++) {
+        float ms = 0.f;
+        CK(cudaEventElapsedTime(&ms, ll.prof_ev[i], ll.prof_ev[i + 1]));
+        if (ll.prof_cat[i] >= 0) ll.prof_ms[ll.prof_cat[i]] += ms;
+        ll.prof_ms[7] += ms;
     }
     return 0;
 }
@@ -660,6 +710,7 @@ static int ll_run_sub(pb200_model * m, std::vector<SubEntry> & es, bool prefill)
     CK(ll_forward(m, b, prefill, d, d + (h_want - h), nW, 0));
     if (nW > 0) CK(cudaMemcpyAsync(ll.logits_host, ll.logits, (size_t) nW * ll.vocab * 4, cudaMemcpyDeviceToHost, m->stream));
     CK(cudaStreamSynchronize(m->stream));
+    CK(prof_collect(m));
     // hand the rows to the caller's order
     for (int i = 0; i < nE; i++) ll.seq_len[(size_t) es[(size_t) i].slot] = es[(size_t) i].pos0 + es[(size_t) i].n;
     ll.rows_tmp.assign(lrows.begin(), lrows.end());
@@ -752,6 +803,11 @@ int ll_debug_read(pb200_model * m, const char * name, float * host, int64_t n) {
     LayerList & ll = *m->ll;
     cudaSetDevice(m->device);
     CK(cudaStreamSynchronize(m->stream));
+    if (strcmp(name, "profile") == 0) {   // ms of the last batch: dense, attention, convolution, scan, norms, element-wise, head, [7] = total
+        if (n > 8) return PB200_EINVAL;
+        memcpy(host, ll.prof_ms, (size_t) n * 4);
+        return 0;
+    }
     if (strcmp(name, "layers") == 0) {
         if (!ll.tap || n > ll.tap_floats) return PB200_EINVAL;
         return (int) cudaMemcpy(host, ll.tap, (size_t) n * 4, cudaMemcpyDeviceToHost);
@@ -883,6 +939,17 @@ int pb200_batch_step(pb200_model * m, int n_entries, const pb200_batch_entry * e
     if (!m) return PB200_EINVAL;
     if (!m->ll) return PB200_ENOTSUP;
     return ll_batch_step(m, n_entries, entries, logits_host, greedy_host);
+}
+int pb200_dense(int type, const void * A, int64_t lda, const void * W, int64_t ldw, float * C, int64_t ldc, int T, int N, int K, const float * bias,
+                const float * resid, int64_t ldr, float alpha, void * stream) {
+    if (type != T_F32 && type != T_BF16) return PB200_ENOTSUP;
+    if (!A || !W || !C || T < 0 || N < 0 || K <= 0 || lda < K || ldw < K || ldc < N || (resid && ldr < N)) return PB200_EINVAL;
+    return launch_dense(type, A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha, (cudaStream_t) stream);
+}
+int pb200_debug_profile(pb200_model * m, int on) {
+    if (!m || !m->ll) return PB200_EINVAL;
+    m->ll->prof_on = on != 0;
+    return 0;
 }
 int pb200_debug_tap_layers(pb200_model * m, int on) {
     if (!m || !m->ll) return PB200_EINVAL;

@@ -409,6 +409,83 @@ __global__ void __launch_bounds__(256) k_mamba2_scan(const float * __restrict__ 
     for (int i = threadIdx.x; i < N * P; i += blockDim.x) gst[i] = S[i];
 }
 
+// The same recurrence with the state in registers: a CTA of 128 threads owns one head and 16 value columns; thread (column pl = tid / 8,
+// part ng = tid % 8) keeps S[n][column] for n = ng, ng + 8, ...  (NREG values).  Tokens are walked in chunks of 16 whose B, C, x rows and
+// step sizes / decays are staged in shared memory by the whole CTA (two CTA barriers per chunk, none per token); y needs one 8-lane
+// shuffle reduction per token.  Used for state sizes up to 128; larger states take k_mamba2_scan.
+constexpr int SCAN_CHUNK = 16, SCAN_COLS = 16;
+template <int NREG>
+__global__ void __launch_bounds__(128) k_mamba2_scan_reg(const float * __restrict__ u, const float * __restrict__ xbc, const int32_t * __restrict__ slot,
+                                                         const int32_t * __restrict__ off, Mamba2Params p, const float * __restrict__ dt_bias,
+                                                         const float * __restrict__ A_log, const float * __restrict__ Dp, float * __restrict__ ssm_state,
+                                                         int64_t slot_stride, float * __restrict__ y) {
+    extern __shared__ float sm[];
+    const int N = p.state, P = p.vdim, inner = mamba2_inner(p), CH = mamba2_conv_channels(p), U = mamba2_in_cols(p);
+    const int ptiles = (P + SCAN_COLS - 1) / SCAN_COLS;
+    const int h = blockIdx.x / ptiles, pt = blockIdx.x - h * ptiles, e = blockIdx.y;
+    const int g = h / (p.heads / p.groups);
+    const int tid = threadIdx.x, pl = tid >> 3, ng = tid & 7;
+    const int pcol = pt * SCAN_COLS + pl;
+    const bool pok = pcol < P;
+    float * Bs = sm;                              // [SCAN_CHUNK][N]
+    float * Cs = Bs + SCAN_CHUNK * N;             // [SCAN_CHUNK][N]
+    float * xs = Cs + SCAN_CHUNK * N;             // [SCAN_CHUNK][SCAN_COLS]
+    float * dts = xs + SCAN_CHUNK * SCAN_COLS;    // [SCAN_CHUNK] step sizes, then [SCAN_CHUNK] decays
+    float * gst = ssm_state + (int64_t) slot[e] * slot_stride + (int64_t) h * N * P;
+    float S[NREG];
+#pragma unroll
+    for (int j = 0; j < NREG; j++) {
+        const int nn = ng + 8 * j;
+        S[j] = (pok && nn < N) ? gst[(int64_t) nn * P + pcol] : 0.f;
+    }
+    const float A = -expf(A_log[h]), dtb = dt_bias[h], Dh = Dp[h];
+    const int t0 = off[e], n = off[e + 1] - t0;
+    for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
+        const int nc = min(SCAN_CHUNK, n - c0);
+        __syncthreads();
+        for (int i = tid; i < nc * N; i += 128) {
+            const int tt = i / N, nn = i - tt * N;
+            const float * row = xbc + (int64_t) (t0 + c0 + tt) * CH + inner + g * N + nn;
+            Bs[i] = row[0];
+            Cs[i] = row[p.groups * N];
+        }
+        for (int i = tid; i < nc * SCAN_COLS; i += 128) {
+            const int tt = i / SCAN_COLS, pp = i - tt * SCAN_COLS;
+            xs[i] = pt * SCAN_COLS + pp < P ? xbc[(int64_t) (t0 + c0 + tt) * CH + h * P + pt * SCAN_COLS + pp] : 0.f;
+        }
+        if (tid < nc) {
+            const float raw = u[(int64_t) (t0 + c0 + tid) * U + 2 * inner + 2 * p.groups * N + h] + dtb;
+            const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+            dts[tid] = dt;
+            dts[SCAN_CHUNK + tid] = expf(A * dt);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nc; tt++) {
+            const float dt = dts[tt], dec = dts[SCAN_CHUNK + tt], xv = xs[tt * SCAN_COLS + pl];
+            const float dx = dt * xv;
+            const float * Br = Bs + tt * N, * Cr = Cs + tt * N;
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < NREG; j++) {
+                const int nn = ng + 8 * j;
+                if (nn < N) {
+                    S[j] = fmaf(dec, S[j], dx * Br[nn]);
+                    acc = fmaf(S[j], Cr[nn], acc);
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            if (ng == 0 && pok) y[(int64_t) (t0 + c0 + tt) * inner + h * P + pcol] = acc + Dh * xv;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NREG; j++) {
+        const int nn = ng + 8 * j;
+        if (pok && nn < N) gst[(int64_t) nn * P + pcol] = S[j];
+    }
+}
+
 template <typename OT>
 __global__ void __launch_bounds__(256) k_mamba2_gate_norm(const float * __restrict__ y, const float * __restrict__ u, Mamba2Params p, const float * __restrict__ w,
                                                           float eps, OT * __restrict__ out) {
@@ -537,6 +614,18 @@ int launch_mamba2_scan(const float * u, const float * xbc, const BatchView & b, 
                        const float * D, float * ssm_state, int64_t slot_stride, float * y, cudaStream_t st) {
     if (b.n_tokens <= 0) return 0;
     if (p.heads <= 0 || p.groups <= 0 || p.heads % p.groups != 0) return (int) cudaErrorInvalidValue;
+    if (p.state <= 128) {
+        const size_t sm2 = ((size_t) 2 * SCAN_CHUNK * p.state + SCAN_CHUNK * SCAN_COLS + 2 * SCAN_CHUNK) * sizeof(float);
+        const dim3 grid2((unsigned) (p.heads * ((p.vdim + SCAN_COLS - 1) / SCAN_COLS)), (unsigned) b.n_entries);
+        const int nreg = (p.state + 7) / 8;
+#define PB_SCAN(NR) return ck_launch([&] { k_mamba2_scan_reg<NR><<<grid2, 128, sm2, st>>>(u, xbc, b.slot, b.off, p, dt_bias, A_log, D, ssm_state, slot_stride, y); })
+        if (nreg <= 1) PB_SCAN(1);
+        if (nreg <= 2) PB_SCAN(2);
+        if (nreg <= 4) PB_SCAN(4);
+        if (nreg <= 8) PB_SCAN(8);
+        PB_SCAN(16);
+#undef PB_SCAN
+    }
     const size_t smem = ((size_t) p.state * p.vdim + 2 * (size_t) p.state + p.vdim) * sizeof(float);
     int rc = raise_smem(k_mamba2_scan, smem);
     if (rc) return rc;

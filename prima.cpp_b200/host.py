@@ -126,6 +126,8 @@ class Lib:
         c.pb200_seq_length.argtypes = [vp, C.c_int]
         c.pb200_batch_step.argtypes = [vp, C.c_int, C.POINTER(BatchEntry), vp, vp]
         c.pb200_debug_tap_layers.argtypes = [vp, C.c_int]
+        c.pb200_debug_profile.argtypes = [vp, C.c_int]
+        c.pb200_dense.argtypes = [C.c_int, vp, i64, vp, i64, vp, i64, C.c_int, C.c_int, C.c_int, vp, vp, i64, f32, vp]
 
     @classmethod
     def get(cls) -> "Lib":
@@ -237,6 +239,13 @@ class Model:
         self.lib.check(self.lib.c.pb200_batch_step(self.h, n, arr, logits.ctypes.data_as(C.c_void_p) if rows else None,
                                                    g.ctypes.data_as(C.c_void_p) if greedy else None), "batch_step")
         return logits, (g.tolist() if greedy else None)
+
+    def profile(self, on: bool = True) -> None:
+        self.lib.check(self.lib.c.pb200_debug_profile(self.h, int(on)), "debug_profile")
+
+    def profile_ms(self) -> dict:
+        v = self.debug_read("profile", 8)
+        return dict(zip(("dense", "attention", "conv", "scan", "norm", "elementwise", "head", "total"), (float(x) for x in v)))
 
     def tap_layers(self, on: bool = True) -> None:
         self.lib.check(self.lib.c.pb200_debug_tap_layers(self.h, int(on)), "debug_tap_layers")
