@@ -23,6 +23,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -119,6 +120,9 @@ struct LayerList {
     std::vector<cudaEvent_t> prof_ev;
     std::vector<int> prof_cat;
     float prof_ms[8] = {0};
+    // decode steps replayed as CUDA graphs, one per (entries, wanted rows); the batch's metadata lives at fixed device addresses
+    struct StepGraph { cudaGraphExec_t exec = nullptr; int seen = 0; uint64_t launches = 0; };
+    std::map<uint64_t, StepGraph> graphs;
     std::vector<int> rows_tmp;      // logits row of the caller (or -(entry+1) for a greedy row) per wanted row of the last sub-batch
 };
 
@@ -453,9 +457,11 @@ int ll_finalize(pb200_model * m) {
     return 0;
 }
 
+static void ll_drop_graphs(LayerList & ll);
 void ll_free(pb200_model * m) {
     LayerList * ll = m->ll;
     if (!ll) return;
+    ll_drop_graphs(*ll);
     for (void * p : ll->scratch) cudaFree(p);
     if (ll->meta_dev) cudaFree(ll->meta_dev);
     if (ll->meta_host) cudaFreeHost(ll->meta_host);
@@ -494,8 +500,15 @@ int ll_seq_length(pb200_model * m, int slot) {
 }
 
 // ---- scratch ----
+static void ll_drop_graphs(LayerList & ll) {
+    for (auto & kv : ll.graphs)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    ll.graphs.clear();
+}
 static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
     LayerList & ll = *m->ll;
+    const bool grow = T > ll.capT || nW > ll.capW || (size_t) 2 * T + 3 * (size_t) nE + 1 + (size_t) nW + 64 > ll.meta_cap;
+    if (grow) ll_drop_graphs(ll);   // captured steps hold the addresses of buffers that are about to move
     if (T > ll.capT || nW > ll.capW) {
         CK(cudaStreamSynchronize(m->stream));
         for (void * p : ll.scratch) cudaFree(p);
@@ -707,7 +720,31 @@ static int ll_run_sub(pb200_model * m, std::vector<SubEntry> & es, bool prefill)
     BatchView b;
     b.n_entries = nE; b.n_tokens = T; b.max_n = max_n;
     b.slot = d + 2 * T; b.off = b.slot + nE; b.pos0 = b.off + nE + 1; b.entry_of = d + T;
-    CK(ll_forward(m, b, prefill, d, d + (h_want - h), nW, 0));
+    static const bool no_graph = getenv("PB200_NO_STEP_GRAPH") != nullptr;
+    bool ran = false;
+    if (!prefill && m->use_graph && !no_graph && !ll.tap_on && !ll.prof_on && T == nE) {
+        LayerList::StepGraph & g = ll.graphs[((uint64_t) nE << 32) | (uint32_t) nW];
+        if (!g.exec && g.seen >= 1 && ll.graphs.size() <= 256) {   // second step of this shape: capture (the first one ran directly and set kernel attributes)
+            cudaGraph_t graph = nullptr;
+            const uint64_t l0 = g_launches.load();
+            if (cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+                const int rc = ll_forward(m, b, false, d, d + (h_want - h), nW, 0);
+                const cudaError_t ce = cudaStreamEndCapture(m->stream, &graph);
+                if (rc == 0 && ce == cudaSuccess && graph && cudaGraphInstantiate(&g.exec, graph, 0) == cudaSuccess) g.launches = g_launches.load() - l0;
+                else g.exec = nullptr;
+                if (graph) cudaGraphDestroy(graph);
+            }
+            cudaGetLastError();   // a failed capture must not poison later calls: direct launches below
+            g_launches -= g_launches.load() - l0;
+        }
+        g.seen++;
+        if (g.exec) {
+            CK(cudaGraphLaunch(g.exec, m->stream));
+            g_launches += g.launches;
+            ran = true;
+        }
+    }
+    if (!ran) CK(ll_forward(m, b, prefill, d, d + (h_want - h), nW, 0));
     if (nW > 0) CK(cudaMemcpyAsync(ll.logits_host, ll.logits, (size_t) nW * ll.vocab * 4, cudaMemcpyDeviceToHost, m->stream));
     CK(cudaStreamSynchronize(m->stream));
     CK(prof_collect(m));

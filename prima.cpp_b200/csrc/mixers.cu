@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include <atomic>
 
@@ -239,11 +240,143 @@ __global__ void __launch_bounds__(AQ * 32) k_attn_window_prefill(const float * _
     }
 }
 
-// decode: one CTA of 4 warps per (head, entry); warp w takes cache rows w*32, w*32+128, ...; partial softmax states merged in shared memory
+// Prompt attention, register-tiled: a CTA of 256 threads owns 64 queries of one (entry, head) and walks key tiles of 64 positions
+// (only tiles some query of the CTA can see: the kept first tokens below the window, then the window up to the diagonal).
+// Thread (ty, tx) = (tid / 16, tid % 16) computes the 4 x 4 block of scores of queries 4 ty .. +3 and keys tx, tx + 16, .. (fp32 FMA over
+// dim from transposed shared-memory tiles), the 16 threads of a query row agree on the running max / sum by shuffles, the weights go to
+// shared memory and every thread accumulates queries 4 ty .. +3 x value columns tx + 16 c.  Everything is fp32.
+constexpr int PQ = 64, PK = 64;
+template <typename OT, int NVC>
+__global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const float * __restrict__ qkvg, const int32_t * __restrict__ off, AttnParams a,
+                                                                   OT * __restrict__ out) {
+    extern __shared__ float sm[];
+    const int e = blockIdx.z, h = blockIdx.y;
+    const int t_begin = off[e], n = off[e + 1] - t_begin;
+    const int q0 = blockIdx.x * PQ;
+    if (q0 >= n) return;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int D = a.dim, DV = a.vdim, C = attn_qkvg_cols(a);
+    const int kvh = h / (a.heads / a.kv_heads);
+    const int koff = a.heads * D + kvh * D, voff = a.heads * D + a.kv_heads * D + kvh * DV, goff = a.heads * D + a.kv_heads * D + a.kv_heads * DV + h;
+    constexpr int PQS = PQ + 4, PKS = PK + 1;   // padded strides: the transposing stores of a tile load spread over the banks
+    float * Qt = sm;                    // [D][PQS]  transposed: Qt[d][q]
+    float * Kt = Qt + D * PQS;          // [D][PKS]  transposed: Kt[d][k]
+    float * Vs = Kt + D * PKS;          // [PK][DV]
+    float * Ps = Vs + PK * DV;          // [PQ][PK + 1]
+    for (int i = tid; i < PQ * D; i += 256) {
+        const int q = i / D, d = i - q * D;
+        Qt[d * PQS + q] = q0 + q < n ? qkvg[(int64_t) (t_begin + q0 + q) * C + h * D + d] * a.scale : 0.f;
+    }
+    const int q_last = min(q0 + PQ, n) - 1;
+    const bool windowed = a.window > 0;
+    const int w_lo = windowed ? max(0, q0 - a.window + 1) : 0;
+    const int s_hi = windowed ? min(a.keep_first, w_lo) : 0;
+    float m[4], l[4], acc[4][NVC];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        m[i] = -INFINITY; l[i] = 0.f;
+#pragma unroll
+        for (int c = 0; c < NVC; c++) acc[i][c] = 0.f;
+    }
+    for (int range = 0; range < 2; range++) {
+        const int lo = range == 0 ? 0 : w_lo, hi = range == 0 ? s_hi : q_last + 1;
+        for (int k0 = lo; k0 < hi; k0 += PK) {
+            const int nk = min(PK, hi - k0);
+            __syncthreads();
+            for (int i = tid; i < PK * D; i += 256) {
+                const int k = i / D, d = i - k * D;
+                Kt[d * PKS + k] = k < nk ? qkvg[(int64_t) (t_begin + k0 + k) * C + koff + d] : 0.f;
+            }
+            for (int i = tid; i < PK * DV; i += 256) {
+                const int k = i / DV, d = i - k * DV;
+                Vs[i] = k < nk ? qkvg[(int64_t) (t_begin + k0 + k) * C + voff + d] : 0.f;
+            }
+            __syncthreads();
+            float s[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) s[i][j] = 0.f;
+            for (int d = 0; d < D; d++) {
+                const float4 qv = *reinterpret_cast<const float4 *>(Qt + d * PQS + ty * 4);
+                float kv[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) kv[j] = Kt[d * PKS + tx + 16 * j];
+                const float qq[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) s[i][j] = fmaf(qq[i], kv[j], s[i][j]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int qi = q0 + ty * 4 + i;
+                float tmax = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int kj = k0 + tx + 16 * j;
+                    const bool valid = tx + 16 * j < nk && kj <= qi && (!windowed || qi - kj < a.window || kj < a.keep_first);
+                    float v = s[i][j];
+                    if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+                    s[i][j] = valid ? v : -INFINITY;
+                    tmax = fmaxf(tmax, s[i][j]);
+                }
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+                const float mn = fmaxf(m[i], tmax);
+                const float corr = (m[i] == -INFINITY || mn == -INFINITY) ? (mn == -INFINITY ? 1.f : 0.f) : expf(m[i] - mn);
+                float psum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float pv = s[i][j] == -INFINITY ? 0.f : expf(s[i][j] - mn);
+                    Ps[(ty * 4 + i) * (PK + 1) + tx + 16 * j] = pv;
+                    psum += pv;
+                }
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+                l[i] = l[i] * corr + psum;
+#pragma unroll
+                for (int c = 0; c < NVC; c++) acc[i][c] *= corr;
+                m[i] = mn;
+            }
+            __syncwarp();   // a query row's weights are written and read by the 16 threads of one half-warp
+            for (int k = 0; k < nk; k++) {
+                float pv[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) pv[i] = Ps[(ty * 4 + i) * (PK + 1) + k];
+#pragma unroll
+                for (int c = 0; c < NVC; c++) {
+                    const int dv = tx + 16 * c;
+                    const float vv = dv < DV ? Vs[k * DV + dv] : 0.f;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) acc[i][c] = fmaf(pv[i], vv, acc[i][c]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int qi = q0 + ty * 4 + i;
+        if (qi >= n) continue;
+        const float gate = sigmoid_f(qkvg[(int64_t) (t_begin + qi) * C + goff]);
+        const float inv = l[i] > 0.f ? gate / l[i] : 0.f;
+#pragma unroll
+        for (int c = 0; c < NVC; c++) {
+            const int dv = tx + 16 * c;
+            if (dv < DV) put(out, (int64_t) (t_begin + qi) * (a.heads * DV) + h * DV + dv, acc[i][c] * inv);
+        }
+    }
+}
+
+// decode: one CTA of 16 warps per (head, entry).  Warp w takes cache rows w, w + 16, ...: the lanes split the key's dimensions (coalesced
+// row reads), the score is a warp sum, the running max / sum are uniform over the warp, and every lane accumulates its share of the value
+// dimensions.  The 16 partial softmax states are merged in shared memory.
+constexpr int DEC_WARPS = 16;
 template <typename OT, int NV>
-__global__ void __launch_bounds__(128) k_attn_window_decode(const float * __restrict__ qkvg, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
-                                                            const int32_t * __restrict__ pos0, AttnParams a, const float * __restrict__ kcache,
-                                                            const float * __restrict__ vcache, int64_t slot_stride, OT * __restrict__ out) {
+__global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const float * __restrict__ qkvg, const int32_t * __restrict__ slot,
+                                                                       const int32_t * __restrict__ off, const int32_t * __restrict__ pos0, AttnParams a,
+                                                                       const float * __restrict__ kcache, const float * __restrict__ vcache,
+                                                                       int64_t slot_stride, OT * __restrict__ out) {
     extern __shared__ float sm[];
     const int e = blockIdx.y, h = blockIdx.x;
     const int t = off[e];
@@ -253,71 +386,67 @@ __global__ void __launch_bounds__(128) k_attn_window_decode(const float * __rest
     const int kvh = h / (a.heads / a.kv_heads);
     const int KD = a.kv_heads * D, VD = a.kv_heads * DV;
     const int keep = min(a.keep_first, a.cache_rows), ring = a.cache_rows - keep;
-    float * qs = sm;                       // [D]
-    float * mm = qs + D;                   // [4] max, [4] sum
-    float * accs = mm + 8;                 // [4][NV*32]
-    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = qkvg[(int64_t) t * C + h * D + d];
+    float * qs = sm;                       // [D], scaled
+    float * mm = qs + ((D + 3) & ~3);      // [DEC_WARPS] max, [DEC_WARPS] sum
+    float * accs = mm + 2 * DEC_WARPS;     // [DEC_WARPS][NV*32]
+    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = qkvg[(int64_t) t * C + h * D + d] * a.scale;
     __syncthreads();
     const float * kc = kcache + (int64_t) slot[e] * slot_stride, * vc = vcache + (int64_t) slot[e] * slot_stride;
     float m = -INFINITY, l = 0.f, acc[NV];
 #pragma unroll
     for (int c = 0; c < NV; c++) acc[c] = 0.f;
     const int rows_used = min(a.cache_rows, pi + 1);
-    for (int r0 = warp * 32; r0 < rows_used; r0 += 128) {
-        const int r = r0 + lane;
+    const bool vec4 = (D & 3) == 0;
+    for (int r = warp; r < rows_used; r += DEC_WARPS) {
         // which position does row r hold right now?
-        int p = -1;
-        if (r < rows_used) {
-            if (r < keep) p = r;
-            else {
-                const int rr = r - keep, ip = pi - keep;       // ip >= 0 here because r < rows_used <= pi + 1
-                p = keep + ip - ((ip - rr) % ring + ring) % ring;
-                if (p < keep) p = -1;
-            }
+        int p;
+        if (r < keep) p = r;
+        else {
+            const int rr = r - keep, ip = pi - keep;           // ip >= 0 here because r < rows_used <= pi + 1
+            p = keep + ip - ((ip - rr) % ring + ring) % ring;
+            if (p < keep) p = -1;
         }
         const bool valid = p >= 0 && p <= pi && (a.window <= 0 || pi - p < a.window || p < a.keep_first);
+        if (!valid) continue;                                   // uniform over the warp
+        const float * kr = kc + (int64_t) r * KD + kvh * D;
         float s = 0.f;
-        if (valid) {
-            const float * kr = kc + (int64_t) r * KD + kvh * D;
-            for (int d = 0; d < D; d++) s = fmaf(qs[d], kr[d], s);
-            s *= a.scale;
-            if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
-        }
-        const float sv = valid ? s : -INFINITY;
-        const float tmax = wmax(sv);
-        if (tmax == -INFINITY) continue;
-        const float mn = fmaxf(m, tmax);
-        const float corr = m == -INFINITY ? 0.f : expf(m - mn);
-        const float p_ = valid ? expf(sv - mn) : 0.f;
-        l = l * corr + wsum(p_);
-#pragma unroll
-        for (int c = 0; c < NV; c++) acc[c] *= corr;
-        for (int j = 0; j < 32; j++) {
-            const float pj = __shfl_sync(0xffffffffu, p_, j);
-            if (pj != 0.f) {
-                const float * vr = vc + (int64_t) (r0 + j) * VD + kvh * DV;
-#pragma unroll
-                for (int c = 0; c < NV; c++) {
-                    const int d = lane + 32 * c;
-                    if (d < DV) acc[c] = fmaf(pj, vr[d], acc[c]);
-                }
+        if (vec4) {
+            for (int d = lane * 4; d < D; d += 128) {
+                const float4 kv = *reinterpret_cast<const float4 *>(kr + d);
+                const float4 qv = *reinterpret_cast<const float4 *>(qs + d);
+                s = fmaf(qv.x, kv.x, s); s = fmaf(qv.y, kv.y, s); s = fmaf(qv.z, kv.z, s); s = fmaf(qv.w, kv.w, s);
             }
+        } else {
+            for (int d = lane; d < D; d += 32) s = fmaf(qs[d], kr[d], s);
+        }
+        s = wsum(s);
+        if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+        const float mn = fmaxf(m, s);
+        const float corr = m == -INFINITY ? 0.f : expf(m - mn);
+        const float pj = expf(s - mn);
+        l = l * corr + pj;
+        const float * vr = vc + (int64_t) r * VD + kvh * DV;
+#pragma unroll
+        for (int c = 0; c < NV; c++) {
+            const int d = lane + 32 * c;
+            acc[c] = fmaf(pj, d < DV ? vr[d] : 0.f, acc[c] * corr);
         }
         m = mn;
     }
-    if (lane == 0) { mm[warp] = m; mm[4 + warp] = l; }
+    if (lane == 0) { mm[warp] = m; mm[DEC_WARPS + warp] = l; }
 #pragma unroll
     for (int c = 0; c < NV; c++) accs[warp * NV * 32 + c * 32 + lane] = acc[c];
     __syncthreads();
     if (warp == 0) {
-        float M = fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3]));
+        float M = -INFINITY;
+        for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, mm[w]);
         float L = 0.f, o[NV];
 #pragma unroll
         for (int c = 0; c < NV; c++) o[c] = 0.f;
-        for (int w = 0; w < 4; w++) {
+        for (int w = 0; w < DEC_WARPS; w++) {
             if (mm[w] == -INFINITY) continue;
             const float f = expf(mm[w] - M);
-            L += mm[4 + w] * f;
+            L += mm[DEC_WARPS + w] * f;
 #pragma unroll
             for (int c = 0; c < NV; c++) o[c] = fmaf(accs[w * NV * 32 + c * 32 + lane], f, o[c]);
         }
@@ -566,6 +695,14 @@ int launch_attn_kv_store(const float * qkvg, const BatchView & b, const AttnPara
         else return (int) cudaErrorInvalidValue;                   \
     } while (0)
 
+template <typename OT, int NVC>
+static int attn_prefill_tiled_typed(const float * qkvg, const BatchView & b, const AttnParams & a, OT * out, cudaStream_t st) {
+    const size_t smem = ((size_t) a.dim * (PQ + 4) + (size_t) a.dim * (PK + 1) + (size_t) PK * a.vdim + (size_t) PQ * (PK + 1)) * sizeof(float);
+    int rc = raise_smem(k_attn_window_prefill_tiled<OT, NVC>, smem);
+    if (rc) return rc;
+    const dim3 grid((unsigned) ((b.max_n + PQ - 1) / PQ), (unsigned) a.heads, (unsigned) b.n_entries);
+    return ck_launch([&] { k_attn_window_prefill_tiled<OT, NVC><<<grid, 256, smem, st>>>(qkvg, b.off, a, out); });
+}
 template <typename OT, int NV>
 static int attn_prefill_typed(const float * qkvg, const BatchView & b, const AttnParams & a, OT * out, cudaStream_t st) {
     const size_t smem = ((size_t) AQ * a.dim + (size_t) AKT * (a.dim + 1) + (size_t) AKT * a.vdim) * sizeof(float);
@@ -577,6 +714,22 @@ static int attn_prefill_typed(const float * qkvg, const BatchView & b, const Att
 int launch_attn_window_prefill(const float * qkvg, const BatchView & b, const AttnParams & a, void * out, int otype, cudaStream_t st) {
     if (b.n_tokens <= 0) return 0;
     if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads != 0 || a.dim <= 0 || a.vdim <= 0) return (int) cudaErrorInvalidValue;
+    static const bool no_tiled = getenv("PB200_ATTN_ROWWISE") != nullptr;   // A/B: the one-warp-per-query kernel for every length
+    if (b.max_n > 16 && !no_tiled) {   // long entries: 64-query tiles; the same numbers up to fp32 summation order
+        const int nvc = (a.vdim + 15) / 16;
+        if (nvc <= 16) {
+            if (otype == T_BF16) {
+                if (nvc <= 2) return attn_prefill_tiled_typed<__nv_bfloat16, 2>(qkvg, b, a, (__nv_bfloat16 *) out, st);
+                if (nvc <= 4) return attn_prefill_tiled_typed<__nv_bfloat16, 4>(qkvg, b, a, (__nv_bfloat16 *) out, st);
+                if (nvc <= 8) return attn_prefill_tiled_typed<__nv_bfloat16, 8>(qkvg, b, a, (__nv_bfloat16 *) out, st);
+                return attn_prefill_tiled_typed<__nv_bfloat16, 16>(qkvg, b, a, (__nv_bfloat16 *) out, st);
+            }
+            if (nvc <= 2) return attn_prefill_tiled_typed<float, 2>(qkvg, b, a, (float *) out, st);
+            if (nvc <= 4) return attn_prefill_tiled_typed<float, 4>(qkvg, b, a, (float *) out, st);
+            if (nvc <= 8) return attn_prefill_tiled_typed<float, 8>(qkvg, b, a, (float *) out, st);
+            return attn_prefill_tiled_typed<float, 16>(qkvg, b, a, (float *) out, st);
+        }
+    }
     const int nv = (a.vdim + 31) / 32;
     if (otype == T_BF16) PB_NV_DISPATCH(nv, return (attn_prefill_typed<__nv_bfloat16, NV>(qkvg, b, a, (__nv_bfloat16 *) out, st)));
     else PB_NV_DISPATCH(nv, return (attn_prefill_typed<float, NV>(qkvg, b, a, (float *) out, st)));
@@ -585,11 +738,11 @@ int launch_attn_window_prefill(const float * qkvg, const BatchView & b, const At
 template <typename OT, int NV>
 static int attn_decode_typed(const float * qkvg, const BatchView & b, const AttnParams & a, const float * kc, const float * vc, int64_t stride, OT * out,
                              cudaStream_t st) {
-    const size_t smem = ((size_t) a.dim + 8 + 4 * NV * 32) * sizeof(float);
+    const size_t smem = ((size_t) ((a.dim + 3) & ~3) + 2 * DEC_WARPS + (size_t) DEC_WARPS * NV * 32) * sizeof(float);
     int rc = raise_smem(k_attn_window_decode<OT, NV>, smem);
     if (rc) return rc;
     const dim3 grid((unsigned) a.heads, (unsigned) b.n_entries);
-    return ck_launch([&] { k_attn_window_decode<OT, NV><<<grid, 128, smem, st>>>(qkvg, b.slot, b.off, b.pos0, a, kc, vc, stride, out); });
+    return ck_launch([&] { k_attn_window_decode<OT, NV><<<grid, DEC_WARPS * 32, smem, st>>>(qkvg, b.slot, b.off, b.pos0, a, kc, vc, stride, out); });
 }
 int launch_attn_window_decode(const float * qkvg, const BatchView & b, const AttnParams & a, const float * kcache, const float * vcache, int64_t slot_stride,
                               void * out, int otype, cudaStream_t st) {

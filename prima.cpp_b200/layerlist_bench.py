@@ -1,0 +1,233 @@
+"""Throughput of the layer-list family (Vamidra) at sizes that resemble a real model's layers, beside the closest existing model
+(the Llama graph over Q4_K weights) at equal width / feed-forward / head counts / number of layer runs, random weights.
+Used by ``bench.py --arch vamidra``; prints one JSON line.
+
+Per size: prompt tokens/s (one sequence of 512 and 2048 tokens) and decode tokens/s (batch 1 and 8 at a 1024-token context) of both
+models through their public entry points (host token ids in, host logits / greedy tokens out), the device time of a prompt and of a
+decode step by kernel category, the like-for-like single-op probes (prompt product: tcgen05 bf16 dense vs tcgen05 k-quant; decode
+product: bf16 weight streaming vs k-quant GEMV) and every kernel's distance from its roofline (measured peaks of MEASURED_PEAKS.json).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+
+SIZES = {
+    "w2048": dict(width=2048, ff=8192, heads=16, kv_heads=4, dim=128, window=1024, keep_first=64, ssm_heads=32, vdim=128, state=128, groups=4,
+                  conv=4, norm_groups=4, vocab=32000),
+    "w4096": dict(width=4096, ff=14336, heads=32, kv_heads=8, dim=128, window=1024, keep_first=64, ssm_heads=64, vdim=128, state=128, groups=8,
+                  conv=4, norm_groups=8, vocab=32000),
+}
+
+
+def vamidra_config(s):
+    att = {"type": "attention", "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+                                           "softcap": 50.0, "mask": {"size": s["window"], "keep_first": s["keep_first"]}},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    ssm = {"type": "mamba2", "mixer": {"heads": s["ssm_heads"], "vdim": s["vdim"], "state": s["state"], "groups": s["groups"], "conv": s["conv"],
+                                        "norm_groups": s["norm_groups"]}, "mlp": {"kind": "dense", "ff": s["ff"]}}
+    # attention, mamba2 repeated twice with shared weights, then one more pair: 6 layer runs
+    return {"architecture": "Vamidra", "width": s["width"], "vocab": s["vocab"], "logit_scale": 1.0, "norm": {"eps": 1e-6},
+            "layers": [att, ssm, dict(att), dict(ssm)], "loop": {"start": 0, "stop": 2, "times": 2}}
+
+
+def dense_shapes(s, cfg):
+    """(N, K) of every dense product of one token through all layer runs (the head not included)."""
+    W, out = s["width"], []
+    order = [0, 1, 0, 1, 2, 3]
+    for t, li in enumerate(order):
+        if li == 0:
+            out += [(W, W), (W, W)]                                        # input mix of a pass: two halves
+        m = cfg["layers"][li]["mixer"]
+        if cfg["layers"][li]["type"] == "attention":
+            out += [(m["heads"] * m["dim"] + 2 * m["kv_heads"] * m["dim"] + m["heads"], W), (W, m["heads"] * m["vdim"])]
+        else:
+            inner = m["heads"] * m["vdim"]
+            out += [(2 * inner + 2 * m["groups"] * m["state"] + m["heads"], W), (W, inner)]
+        out += [(2 * s["ff"], W), (W, s["ff"])]
+    return out
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def run(args, pkg, lib):
+    import numpy as np
+    import torch
+    hbm, tflops, src = peaks()
+    ptr = lambda t: C.c_void_p(t.data_ptr())   # noqa: E731
+    sync = torch.cuda.synchronize
+    res = {"metric": "Vamidra prompt / decode throughput beside the Llama graph at equal size", "impl": "b200", "arch": "Vamidra", "n_gpus": 1,
+           "dtype": "bf16", "data": "synthetic random weights", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}, "sizes": {}}
+    rng = np.random.default_rng(0)
+
+    def timed(fn, reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        sync()
+        return e0.elapsed_time(e1) / reps
+
+    for key in ([args.arch_size] if args.arch_size != "all" else list(SIZES)):
+        s = SIZES[key]
+        cfg = vamidra_config(s)
+        out = {"config": {k: s[k] for k in ("width", "ff", "heads", "kv_heads", "window", "keep_first", "ssm_heads", "state")}, "layer_runs": 6}
+        # ---------------- the new design ----------------
+        m = pkg.Model.from_config(cfg, dtype="bfloat16", n_ctx=4096, n_seq=16)
+        m.synth(0, 7)
+        m.finalize()
+        shapes = dense_shapes(s, cfg)
+        flops_tok = 2.0 * sum(n * k for n, k in shapes)
+        wbytes = 2.0 * sum(n * k for n, k in shapes) + 2.0 * s["vocab"] * s["width"]
+        v = {}
+        for T in (512, 2048):
+            toks = rng.integers(0, s["vocab"], T).tolist()
+
+            def prompt():
+                sl = m.seq_alloc()
+                m.batch_step([(sl, toks, [T - 1])])
+                m.seq_free(sl)
+            for _ in range(3):
+                prompt()
+            t0 = time.perf_counter()
+            reps = max(3, args.steps // 16)
+            for _ in range(reps):
+                prompt()
+            dt = (time.perf_counter() - t0) / reps
+            v[f"prompt{T}_tok_s"] = T / dt
+            m.profile(True)
+            prompt()
+            pm = m.profile_ms()
+            m.profile(False)
+            v[f"prompt{T}_device_ms"] = pm
+            v[f"prompt{T}_dense_tflops"] = flops_tok * T / pm["dense"] / 1e9
+            v[f"prompt{T}_dense_frac_of_tensor_peak"] = v[f"prompt{T}_dense_tflops"] / tflops
+            # attention: 4 * dim * visible keys per query and head; 3 attention runs
+            vis = sum(min(i + 1, s["window"]) + max(0, min(s["keep_first"], i + 1 - s["window"])) for i in range(T))
+            v[f"prompt{T}_attention_tflops"] = 3 * 4.0 * s["dim"] * s["heads"] * vis / pm["attention"] / 1e9
+            # scan: bytes that must move (conv outputs read, y written, step sizes), 3 mamba runs
+            inner, ch = s["ssm_heads"] * s["vdim"], s["ssm_heads"] * s["vdim"] + 2 * s["groups"] * s["state"]
+            v[f"prompt{T}_scan_gbs"] = 3 * T * 4.0 * (ch + inner + s["ssm_heads"]) / pm["scan"] / 1e6
+            v[f"prompt{T}_scan_gflops"] = 3 * T * 6.0 * s["ssm_heads"] * s["state"] * s["vdim"] / pm["scan"] / 1e6
+        for B in (1, 8):
+            slots = [m.seq_alloc() for _ in range(B)]
+            ctx = rng.integers(0, s["vocab"], 1024).tolist()
+            m.batch_step([(sl, ctx, []) for sl in slots])
+            step = lambda: m.batch_step([(sl, [5], []) for sl in slots], greedy=True)   # noqa: E731
+            for _ in range(max(3, args.warmup)):
+                step()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                step()
+            dt = (time.perf_counter() - t0) / args.steps
+            v[f"decode_b{B}_tok_s"] = B / dt
+            v[f"decode_b{B}_ms_per_step"] = dt * 1e3
+            v[f"decode_b{B}_whole_step_frac_of_hbm_peak"] = wbytes / dt / 1e9 / hbm
+            m.profile(True)
+            step()
+            pm = m.profile_ms()
+            m.profile(False)
+            v[f"decode_b{B}_device_ms"] = pm
+            v[f"decode_b{B}_dense_gbs"] = (wbytes - 2.0 * s["vocab"] * s["width"]) / pm["dense"] / 1e6
+            v[f"decode_b{B}_dense_frac_of_hbm_peak"] = v[f"decode_b{B}_dense_gbs"] / hbm
+            for sl in slots:
+                m.seq_free(sl)
+        v["weight_bytes_per_token"] = wbytes
+        m.close()
+        out["vamidra"] = v
+        # ---------------- the closest existing model: the Llama graph, Q4_K, equal sizes, 6 layers ----------------
+        hp = pkg.HParams(n_layer=6, n_embd=s["width"], n_head=s["heads"], n_head_kv=s["kv_heads"], head_dim=128, n_ff=s["ff"], n_vocab=s["vocab"],
+                         n_ctx=4096, rope_mode=0, n_ctx_orig=8192, rope_freq_base=500000.0, rope_freq_scale=1.0, rms_eps=1e-5)
+        eng = pkg.Model(hp)
+        eng.synth(0, 11)
+        eng.finalize()
+        w = {}
+        logits = np.empty(s["vocab"], dtype=np.float32)
+        for T in (512, 2048):
+            toks = rng.integers(0, s["vocab"], T).astype(np.int32)
+            for _ in range(3):
+                eng.prefill(toks, 0, logits)
+            t0 = time.perf_counter()
+            reps = max(3, args.steps // 16)
+            for _ in range(reps):
+                eng.prefill(toks, 0, logits)
+            w[f"prompt{T}_tok_s"] = T / ((time.perf_counter() - t0) / reps)
+        eng.prefill(rng.integers(0, s["vocab"], 1024).astype(np.int32), 0, logits)
+        for i in range(max(3, args.warmup)):
+            eng.decode(5, 1024 + i, logits)
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            eng.decode(5, 1100 + i, logits)
+        dt = (time.perf_counter() - t0) / args.steps
+        w["decode_b1_tok_s"] = 1.0 / dt
+        w["decode_b1_whole_step_frac_of_hbm_peak"] = eng.weight_bytes / dt / 1e9 / hbm
+        pr = eng.profile_step(5, 1300)
+        w["decode_b1_gemv_gbs"] = pr["gemv_bytes"] / pr["gemv_ms"] / 1e6
+        w["decode_b1_gemv_frac_of_hbm_peak"] = w["decode_b1_gemv_gbs"] / hbm
+        w["weight_bytes_per_token"] = eng.weight_bytes
+        eng.close()
+        out["llama_q4_k"] = w
+        # ---------------- like-for-like single-op probes at the feed-forward shapes ----------------
+        probes = {}
+        for name, (N, K) in (("gate_up", (2 * s["ff"], s["width"])), ("down", (s["width"], s["ff"]))):
+            for T in (512, 2048):
+                A = torch.randn((T, K), device="cuda").to(torch.bfloat16)
+                Wd = (torch.randn((N, K), device="cuda") / K ** 0.5).to(torch.bfloat16)
+                Cd = torch.empty((T, N), device="cuda")
+                f = lambda: lib.c.pb200_dense(30, ptr(A), K, ptr(Wd), K, ptr(Cd), N, T, N, K, None, None, 0, 1.0, None)   # noqa: E731
+                for _ in range(3):
+                    f()
+                ms = timed(f, 10)
+                rb = lib.c.pb200_row_bytes(12, K)
+                Wq = torch.randint(0, 255, (N * rb + 64,), dtype=torch.uint8, device="cuda")
+                xd = torch.randn((T, K), device="cuda")
+                ws = torch.zeros(lib.c.pb200_mul_mat_q_workspace_bytes(K, T) + 64, dtype=torch.uint8, device="cuda")
+                g = lambda: lib.c.pb200_mul_mat_q(12, ptr(Wq), N, K, ptr(xd), K, T, ptr(Cd), None, None, ptr(ws), None)   # noqa: E731
+                for _ in range(3):
+                    g()
+                ms_q = timed(g, 10)
+                fl = 2.0 * N * K * T
+                probes[f"prompt_product_{name}_T{T}"] = {"dense_bf16_tflops": fl / ms / 1e9, "dense_bf16_frac_of_tensor_peak": fl / ms / 1e9 / tflops,
+                                                         "kquant_q4_K_tflops": fl / ms_q / 1e9, "kquant_q4_K_frac_of_tensor_peak": fl / ms_q / 1e9 / tflops}
+                del A, Wd, Cd, Wq, xd, ws
+            # decode product: weights larger than L2 are streamed once per call
+            for T in (1, 8):
+                A = torch.randn((T, K), device="cuda").to(torch.bfloat16)
+                Wd = (torch.randn((N, K), device="cuda") / K ** 0.5).to(torch.bfloat16)
+                Cd = torch.empty((T, N), device="cuda")
+                f = lambda: lib.c.pb200_dense(30, ptr(A), K, ptr(Wd), K, ptr(Cd), N, T, N, K, None, None, 0, 1.0, None)   # noqa: E731
+                for _ in range(3):
+                    f()
+                ms = timed(f, 20)
+                probes[f"decode_product_{name}_b{T}"] = {"dense_bf16_gbs": 2.0 * N * K / ms / 1e6, "dense_bf16_frac_of_hbm_peak": 2.0 * N * K / ms / 1e6 / hbm}
+                if T == 1:
+                    rb = lib.c.pb200_row_bytes(12, K)
+                    Wq = torch.randint(0, 255, (N * rb + 64,), dtype=torch.uint8, device="cuda")
+                    xd = torch.randn((K,), device="cuda")
+                    yd = torch.empty((N,), device="cuda")
+                    aw = torch.zeros(lib.c.pb200_act_workspace_bytes(K) + 64, dtype=torch.uint8, device="cuda")
+                    g = lambda: lib.c.pb200_mul_mat_vec(12, ptr(Wq), N, K, ptr(xd), ptr(yd), ptr(aw), None)   # noqa: E731
+                    for _ in range(3):
+                        g()
+                    ms_q = timed(g, 20)
+                    probes[f"decode_product_{name}_b{T}"].update({"kquant_q4_K_gbs": N * rb / ms_q / 1e6, "kquant_q4_K_frac_of_hbm_peak": N * rb / ms_q / 1e6 / hbm})
+                    del Wq, xd, yd, aw
+                del A, Wd, Cd
+        out["like_kernels"] = probes
+        res["sizes"][key] = out
+        torch.cuda.empty_cache()
+    res["gpu_launches"] = int(lib.c.pb200_kernel_launches())
+    print(json.dumps(res))
+    return res
