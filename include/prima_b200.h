@@ -238,8 +238,8 @@ PB200_API int pb200_debug_read(pb200_model * m, const char * name, float * host,
 PB200_API int pb200_set_use_graph(pb200_model * m, int on);             /* CUDA-graph replay on/off (default on) */
 
 /* dense product, device buffers: C[t][n] = alpha * sum_k A[t][k] W[n][k] (+ bias[n]) (+ resid[t][n]); A [T][K] and W [N][K] row-major of `type`
- * (PB200_TYPE_F32: true fp32; PB200_TYPE_BF16: bf16 operands, fp32 accumulation: tcgen05 tensor cores for more than 8 tokens when K and
- * the strides are multiples of 8, a weight-streaming kernel for up to 8 tokens); C, bias, resid f32; resid may alias C; strides in elements */
+ * (PB200_TYPE_F32: true fp32; PB200_TYPE_BF16: bf16 operands, fp32 accumulation: tcgen05 tensor cores for more than 4 tokens when K and
+ * the strides are multiples of 8, a weight-streaming kernel for fewer); C, bias, resid f32; resid may alias C; strides in elements */
 PB200_API int pb200_dense(int type, const void * A, int64_t lda, const void * W, int64_t ldw, float * C, int64_t ldc, int T, int N, int K,
                           const float * bias, const float * resid, int64_t ldr, float alpha, void * stream);
 

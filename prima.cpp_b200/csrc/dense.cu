@@ -1,15 +1,16 @@
 // prima.cpp_b200/csrc/dense.cu — products with dense f32 / bf16 weight matrices stored [out][in]:
 //   C[t][n] = alpha * sum_k A[t][k] W[n][k] (+ bias[n]) (+ resid[t][n])
 // Three kernels behind one launcher:
-//   k_dense_rows   few tokens (decode batches): one warp streams one weight row with 16-byte loads and keeps one fp32 accumulator per token;
+//   k_dense_rows   up to 4 tokens (decode): one warp streams one weight row with 16-byte loads and keeps one fp32 accumulator per token;
 //                  the launch is bound by the HBM read of W
-//   k_dense_tc     bf16, many tokens (prompts): tcgen05.mma with the accumulator in TMEM (dense_tc.cu)
+//   k_dense_tc     bf16, 5 tokens and more (decode batches, prompts): tcgen05.mma with the accumulator in TMEM (dense_tc.cu)
 //   k_dense_tile   everything else (true-fp32 products, ragged shapes): shared-memory tiles, fp32 fused multiply-add
 // No kernel splits K across CTAs or uses atomics: an output element is one fixed-order sum, whatever else is in the batch.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 
 #include "layers.h"
 
@@ -149,6 +150,17 @@ __global__ void __launch_bounds__(256) k_dense_rows(const WT * __restrict__ A, i
 }
 
 constexpr int ROWS_MAX_T = 8;
+// Largest batch the weight-streaming kernel takes when the tensor-core kernel could run instead.  Measured on a B200 at 28672 x 4096 bf16:
+// 8 tokens stream at 1.9 TB/s through this kernel (one L1 read of the activations per token and weight chunk) and at 3.3 TB/s through
+// the tensor-core kernel's 64-token tile, so the hand-over is at 4.  PB200_DENSE_ROWS_MAX overrides for A/B runs.
+int rows_max_t() {
+    static const int v = [] {
+        const char * e = getenv("PB200_DENSE_ROWS_MAX");
+        const int n = e ? atoi(e) : 4;
+        return n < 0 ? 0 : (n > ROWS_MAX_T ? ROWS_MAX_T : n);
+    }();
+    return v;
+}
 
 template <typename WT>
 int dense_typed(const WT * A, int64_t lda, const WT * W, int64_t ldw, float * C, int64_t ldc, int T, int N, int K, const float * bias,
@@ -179,7 +191,7 @@ int dense_typed(const WT * A, int64_t lda, const WT * W, int64_t ldw, float * C,
 }  // namespace
 
 int dense_uses_tensor_cores(int type, int T, int N, int K, int64_t lda, int64_t ldw) {
-    return type == T_BF16 && T > ROWS_MAX_T && dense_tc_ok(T, N, K, lda, ldw, nullptr, nullptr) ? 1 : 0;
+    return type == T_BF16 && T > rows_max_t() && dense_tc_ok(T, N, K, lda, ldw, nullptr, nullptr) ? 1 : 0;
 }
 
 int launch_dense(int type, const void * A, int64_t lda, const void * W, int64_t ldw, float * C, int64_t ldc, int T, int N, int K, const float * bias,
@@ -188,7 +200,7 @@ int launch_dense(int type, const void * A, int64_t lda, const void * W, int64_t 
     if (K <= 0 || !A || !W || !C) return (int) cudaErrorInvalidValue;
     if (type == 0 /* T_F32 */) return dense_typed<float>((const float *) A, lda, (const float *) W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha, st);
     if (type != T_BF16) return (int) cudaErrorInvalidValue;
-    if (T > ROWS_MAX_T && dense_tc_ok(T, N, K, lda, ldw, A, W))
+    if (T > rows_max_t() && dense_tc_ok(T, N, K, lda, ldw, A, W))
         return launch_dense_tc((const __nv_bfloat16 *) A, lda, (const __nv_bfloat16 *) W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha, st);
     return dense_typed<__nv_bfloat16>((const __nv_bfloat16 *) A, lda, (const __nv_bfloat16 *) W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha, st);
 }

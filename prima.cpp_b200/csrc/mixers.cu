@@ -6,6 +6,7 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <algorithm>
 #include <atomic>
 
 #include "layers.h"
@@ -470,7 +471,7 @@ __global__ void k_mamba2_conv(const float * __restrict__ u, const int32_t * __re
     const int lt = t - off[e];
     const int CH = mamba2_conv_channels(p), U = mamba2_in_cols(p), inner = mamba2_inner(p), taps = p.conv;
     const float * st = conv_state + (int64_t) slot[e] * slot_stride;   // [taps-1][CH], row taps-2 = the input just before this entry
-    for (int c = threadIdx.x; c < CH; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < CH; c += gridDim.y * blockDim.x) {
         float acc = bias[c];
         for (int d = 0; d < taps; d++) {
             const int l2 = lt - d;
@@ -538,11 +539,12 @@ __global__ void __launch_bounds__(256) k_mamba2_scan(const float * __restrict__ 
     for (int i = threadIdx.x; i < N * P; i += blockDim.x) gst[i] = S[i];
 }
 
-// The same recurrence with the state in registers: a CTA of 128 threads owns one head and 16 value columns; thread (column pl = tid / 8,
-// part ng = tid % 8) keeps S[n][column] for n = ng, ng + 8, ...  (NREG values).  Tokens are walked in chunks of 16 whose B, C, x rows and
+// The same recurrence with the state in registers: a CTA of 128 threads owns one head and 32 value columns; thread (pl = tid / 8,
+// part ng = tid % 8) keeps S[n][column] for columns pl and pl + 16 and n = ng, ng + 8, ...  (2 x NREG values; a B / C value read from
+// shared memory serves both columns).  Tokens are walked in chunks of 16 whose B, C, x rows and
 // step sizes / decays are staged in shared memory by the whole CTA (two CTA barriers per chunk, none per token); y needs one 8-lane
 // shuffle reduction per token.  Used for state sizes up to 128; larger states take k_mamba2_scan.
-constexpr int SCAN_CHUNK = 16, SCAN_COLS = 16;
+constexpr int SCAN_CHUNK = 16, SCAN_COLS = 32;
 template <int NREG>
 __global__ void __launch_bounds__(128) k_mamba2_scan_reg(const float * __restrict__ u, const float * __restrict__ xbc, const int32_t * __restrict__ slot,
                                                          const int32_t * __restrict__ off, Mamba2Params p, const float * __restrict__ dt_bias,
@@ -554,18 +556,19 @@ __global__ void __launch_bounds__(128) k_mamba2_scan_reg(const float * __restric
     const int h = blockIdx.x / ptiles, pt = blockIdx.x - h * ptiles, e = blockIdx.y;
     const int g = h / (p.heads / p.groups);
     const int tid = threadIdx.x, pl = tid >> 3, ng = tid & 7;
-    const int pcol = pt * SCAN_COLS + pl;
-    const bool pok = pcol < P;
+    const int pcol = pt * SCAN_COLS + pl, pcol1 = pcol + 16;
+    const bool pok = pcol < P, pok1 = pcol1 < P;
     float * Bs = sm;                              // [SCAN_CHUNK][N]
     float * Cs = Bs + SCAN_CHUNK * N;             // [SCAN_CHUNK][N]
     float * xs = Cs + SCAN_CHUNK * N;             // [SCAN_CHUNK][SCAN_COLS]
     float * dts = xs + SCAN_CHUNK * SCAN_COLS;    // [SCAN_CHUNK] step sizes, then [SCAN_CHUNK] decays
     float * gst = ssm_state + (int64_t) slot[e] * slot_stride + (int64_t) h * N * P;
-    float S[NREG];
+    float S[NREG], S1[NREG];
 #pragma unroll
     for (int j = 0; j < NREG; j++) {
         const int nn = ng + 8 * j;
         S[j] = (pok && nn < N) ? gst[(int64_t) nn * P + pcol] : 0.f;
+        S1[j] = (pok1 && nn < N) ? gst[(int64_t) nn * P + pcol1] : 0.f;
     }
     const float A = -expf(A_log[h]), dtb = dt_bias[h], Dh = Dp[h];
     const int t0 = off[e], n = off[e + 1] - t0;
@@ -590,28 +593,36 @@ __global__ void __launch_bounds__(128) k_mamba2_scan_reg(const float * __restric
         }
         __syncthreads();
         for (int tt = 0; tt < nc; tt++) {
-            const float dt = dts[tt], dec = dts[SCAN_CHUNK + tt], xv = xs[tt * SCAN_COLS + pl];
-            const float dx = dt * xv;
+            const float dt = dts[tt], dec = dts[SCAN_CHUNK + tt], xv = xs[tt * SCAN_COLS + pl], xv1 = xs[tt * SCAN_COLS + pl + 16];
+            const float dx = dt * xv, dx1 = dt * xv1;
             const float * Br = Bs + tt * N, * Cr = Cs + tt * N;
-            float acc = 0.f;
+            float acc = 0.f, acc1 = 0.f;
 #pragma unroll
             for (int j = 0; j < NREG; j++) {
                 const int nn = ng + 8 * j;
                 if (nn < N) {
-                    S[j] = fmaf(dec, S[j], dx * Br[nn]);
-                    acc = fmaf(S[j], Cr[nn], acc);
+                    const float bv = Br[nn], cv = Cr[nn];
+                    S[j] = fmaf(dec, S[j], dx * bv);
+                    S1[j] = fmaf(dec, S1[j], dx1 * bv);
+                    acc = fmaf(S[j], cv, acc);
+                    acc1 = fmaf(S1[j], cv, acc1);
                 }
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
             acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 4);
             if (ng == 0 && pok) y[(int64_t) (t0 + c0 + tt) * inner + h * P + pcol] = acc + Dh * xv;
+            if (ng == 0 && pok1) y[(int64_t) (t0 + c0 + tt) * inner + h * P + pcol1] = acc1 + Dh * xv1;
         }
     }
 #pragma unroll
     for (int j = 0; j < NREG; j++) {
         const int nn = ng + 8 * j;
         if (pok && nn < N) gst[(int64_t) nn * P + pcol] = S[j];
+        if (pok1 && nn < N) gst[(int64_t) nn * P + pcol1] = S1[j];
     }
 }
 
@@ -758,7 +769,10 @@ int launch_mamba2_conv(const float * u, const BatchView & b, const Mamba2Params 
                        int64_t slot_stride, float * xbc, cudaStream_t st) {
     if (b.n_tokens <= 0) return 0;
     if (p.conv < 1) return (int) cudaErrorInvalidValue;
-    int rc = ck_launch([&] { k_mamba2_conv<<<b.n_tokens, 256, 0, st>>>(u, b.slot, b.off, b.entry_of, p, w, bias, conv_state, slot_stride, xbc); });
+    // few tokens (decode): spread the channels of a token over several CTAs
+    const int CHn = mamba2_conv_channels(p);
+    const dim3 cgrid((unsigned) b.n_tokens, (unsigned) (b.n_tokens >= 64 ? 1 : std::min(16, (CHn + 255) / 256)));
+    int rc = ck_launch([&] { k_mamba2_conv<<<cgrid, 256, 0, st>>>(u, b.slot, b.off, b.entry_of, p, w, bias, conv_state, slot_stride, xbc); });
     if (rc || p.conv < 2) return rc;
     const dim3 grid((unsigned) ((mamba2_conv_channels(p) + 127) / 128), (unsigned) b.n_entries);
     return ck_launch([&] { k_mamba2_conv_state<<<grid, 128, 0, st>>>(u, b.slot, b.off, p, conv_state, slot_stride); });

@@ -225,6 +225,21 @@ def run(args, pkg, lib):
                     probes[f"decode_product_{name}_b{T}"].update({"kquant_q4_K_gbs": N * rb / ms_q / 1e6, "kquant_q4_K_frac_of_hbm_peak": N * rb / ms_q / 1e6 / hbm})
                     del Wq, xd, yd, aw
                 del A, Wd, Cd
+        # prompt attention: the Llama graph's tiled kernel (every earlier position, f16 cache) against the windowed kernel's share of a prompt
+        T, H, HK = 2048, s["heads"], s["kv_heads"]
+        q = torch.randn((T, H * 128), device="cuda")
+        kc = torch.randn((T, HK * 128), device="cuda").to(torch.float16)
+        vc = torch.randn((T, HK * 128), device="cuda").to(torch.float16)
+        o = torch.empty((T, H * 128), device="cuda")
+        pos = torch.arange(T, dtype=torch.int32, device="cuda")
+        f = lambda: lib.c.pb200_attn_prefill(ptr(q), ptr(kc), ptr(vc), ptr(o), H, HK, 128, ptr(pos), T, T, 128 ** -0.5, None)   # noqa: E731
+        for _ in range(3):
+            f()
+        ms = timed(f, 10)
+        probes["prompt_attention_T2048"] = {"llama_causal_tflops": 4.0 * 128 * H * T * (T + 1) / 2 / ms / 1e9, "llama_ms": ms,
+                                            "vamidra_windowed_tflops": v["prompt2048_attention_tflops"],
+                                            "vamidra_ms_per_run": v["prompt2048_device_ms"]["attention"] / 3}
+        del q, kc, vc, o, pos
         out["like_kernels"] = probes
         res["sizes"][key] = out
         torch.cuda.empty_cache()
