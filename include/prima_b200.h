@@ -257,7 +257,7 @@ PB200_API int          pb200_arch_family(const char * name);
  * products on bf16 operands with fp32 accumulation; norms, attention scores and weights, the residual stream and all recurrent state stay
  * fp32) or PB200_TYPE_F32 (everything in true fp32).  n_ctx: the most positions one sequence can have where a layer has to keep all of
  * them; a windowed attention layer keeps keep_first + window rows per sequence whatever its length.  n_seq: sequence slots
- * (<= 0: as many as 8 GiB of state hold, 4 .. 64).  Tensors arrive through pb200_model_set_tensor under their checkpoint names with
+ * (<= 0: as many as 8 GiB of state hold, 4 .. 256).  Tensors arrive through pb200_model_set_tensor under their checkpoint names with
  * type PB200_TYPE_BF16 or PB200_TYPE_F32 (converted to what the model computes in); then pb200_model_finalize.  pb200_model_synth
  * fills every tensor with random values instead (benchmarks). */
 PB200_API pb200_model * pb200_model_create_from_config(const char * config_json, int compute_type, int device, int n_ctx, int n_seq);

@@ -444,9 +444,9 @@ int ll_finalize(pb200_model * m) {
         off = (off + 3) / 4 * 4;
     }
     ll.slot_floats = std::max<int64_t>(off, 4);
-    if (ll.n_seq <= 0) {   // as many slots as 8 GiB of state hold, between 4 and 64
+    if (ll.n_seq <= 0) {   // as many slots as 8 GiB of state hold, between 4 and 256
         const int64_t fit = (int64_t) (8ll << 30) / (ll.slot_floats * 4);
-        ll.n_seq = (int) std::min<int64_t>(64, std::max<int64_t>(4, fit));
+        ll.n_seq = (int) std::min<int64_t>(256, std::max<int64_t>(4, fit));
     }
     CK(m->alloc((void **) &ll.state, (size_t) ll.slot_floats * 4 * (size_t) ll.n_seq));
     CK(cudaMemset(ll.state, 0, (size_t) ll.slot_floats * 4 * (size_t) ll.n_seq));
@@ -939,7 +939,12 @@ int pb200_model_load_dir(const char * dir, int compute_type, int device, int n_c
         const uint64_t lo = (uint64_t) offs->arr[0].num, hi = (uint64_t) offs->arr[1].num;
         if (lo > hi || hi > dsz) { rc = PB200_EINVAL; break; }
         const int type = dt == "BF16" ? T_BF16 : dt == "F32" ? T_F32 : -1;
-        if (type < 0) { rc = PB200_ENOTSUP; break; }
+        TensorPlace pl;
+        if (!m->ll->arch->resolve(*m->ll, name, pl)) {   // a tensor the design has no place for is left out; finalize still refuses an incomplete model
+            fprintf(stderr, "[pb200] tensor '%s' is not part of %s: skipped\n", name.c_str(), arch->name);
+            continue;
+        }
+        if (type < 0) { rc = PB200_ENOTSUP; fprintf(stderr, "[pb200] tensor '%s': dtype %s\n", name.c_str(), dt.c_str()); break; }
         rc = pb200_model_set_tensor(m, name.c_str(), type, data + lo, (size_t) (hi - lo));
         if (rc) fprintf(stderr, "[pb200] tensor '%s': %s\n", name.c_str(), pb200_error_string(rc));
     }

@@ -726,7 +726,8 @@ int launch_attn_window_prefill(const float * qkvg, const BatchView & b, const At
     if (b.n_tokens <= 0) return 0;
     if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads != 0 || a.dim <= 0 || a.vdim <= 0) return (int) cudaErrorInvalidValue;
     static const bool no_tiled = getenv("PB200_ATTN_ROWWISE") != nullptr;   // A/B: the one-warp-per-query kernel for every length
-    if (b.max_n > 16 && !no_tiled) {   // long entries: 64-query tiles; the same numbers up to fp32 summation order
+    const size_t tiled_smem = ((size_t) a.dim * (PQ + 4) + (size_t) a.dim * (PK + 1) + (size_t) PK * a.vdim + (size_t) PQ * (PK + 1)) * sizeof(float);
+    if (b.max_n > 16 && !no_tiled && tiled_smem <= 220 * 1024) {   // long entries: 64-query tiles; the same numbers up to fp32 summation order
         const int nvc = (a.vdim + 15) / 16;
         if (nvc <= 16) {
             if (otype == T_BF16) {
