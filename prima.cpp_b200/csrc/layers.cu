@@ -595,6 +595,7 @@ static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const 
     const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
     CK(launch_embed(ll.embed.data, ct, W, tokens_dev, T, ll.x, ll.x0, st));
     float * x = ll.x, * xalt = ll.xalt;
+    bool act_ready = false;
     if (ll.tap_on) {
         const int64_t need = (int64_t) ll.runs.size() * T * W;
         if (need > ll.tap_cap) {
@@ -621,8 +622,13 @@ static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const 
             std::swap(x, xalt);
         }
         float * sbase = ll.state + r.state_off;
-        CAT(CAT_NORM);
-        CK(launch_layernorm(x, nullptr, L.norm1.data, ll.eps, ll.act, ct, T, W, st));
+        if (!act_ready) {   // otherwise the previous run's closing norm has already left layernorm(x) * norm1 in ll.act
+            CAT(CAT_NORM);
+            CK(launch_layernorm(x, nullptr, L.norm1.data, ll.eps, ll.act, ct, T, W, st));
+        }
+        act_ready = false;
+        // the norm that closes this run also opens the next one, unless a pass of the repeated block (its input mix) or the end comes first
+        const LLayer * nextL = (ir + 1 < ll.runs.size() && ll.runs[ir + 1].pass < 0) ? &ll.layers[(size_t) ll.runs[ir + 1].layer] : nullptr;
         if (L.kind == MIX_ATTENTION) {
             const AttnParams & a = L.att;
             const int C = attn_qkvg_cols(a);
@@ -652,10 +658,10 @@ static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const 
             CK(launch_dense(ct, ll.act, inner, L.out.data, inner, ll.msub, W, T, W, inner, nullptr, nullptr, 0, 1.f, st));
         }
         CAT(CAT_NORM);
-        CK(launch_layernorm_residual(ll.msub, L.norm1b.data, ll.eps, x, T, W, st));
+        if (L.ff > 0) CK(launch_layernorm_residual_next(ll.msub, L.norm1b.data, L.norm2.data, ll.eps, x, ll.act, ct, T, W, st));
+        else if (nextL) { CK(launch_layernorm_residual_next(ll.msub, L.norm1b.data, nextL->norm1.data, ll.eps, x, ll.act, ct, T, W, st)); act_ready = true; }
+        else CK(launch_layernorm_residual(ll.msub, L.norm1b.data, ll.eps, x, T, W, st));
         if (L.ff > 0) {
-            CAT(CAT_NORM);
-            CK(launch_layernorm(x, nullptr, L.norm2.data, ll.eps, ll.act, ct, T, W, st));
             CAT(CAT_DENSE);
             CK(launch_dense(ct, ll.act, W, L.gateup.data, W, ll.big, 2 * L.ff, T, 2 * L.ff, W, nullptr, nullptr, 0, 1.f, st));
             CAT(CAT_ELEM);
@@ -663,7 +669,8 @@ static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const 
             CAT(CAT_DENSE);
             CK(launch_dense(ct, ll.act, L.ff, L.down.data, L.ff, ll.msub, W, T, W, L.ff, nullptr, nullptr, 0, 1.f, st));
             CAT(CAT_NORM);
-            CK(launch_layernorm_residual(ll.msub, L.norm2b.data, ll.eps, x, T, W, st));
+            if (nextL) { CK(launch_layernorm_residual_next(ll.msub, L.norm2b.data, nextL->norm1.data, ll.eps, x, ll.act, ct, T, W, st)); act_ready = true; }
+            else CK(launch_layernorm_residual(ll.msub, L.norm2b.data, ll.eps, x, T, W, st));
         }
         if (ll.tap_on) CK(cudaMemcpyAsync(ll.tap + (int64_t) ir * T * W, x, (size_t) T * W * 4, cudaMemcpyDeviceToDevice, st));
     }

@@ -40,6 +40,9 @@ int launch_cast(const float * x, void * y, int otype, int64_t n, cudaStream_t st
 int launch_layernorm(const float * x, const int32_t * rows, const float * w, float eps, void * y, int otype, int n_rows, int width, cudaStream_t stream);
 // x[t] += layernorm(m[t]) * w      (the post-norm of a sublayer and the residual sum, fp32)
 int launch_layernorm_residual(const float * m, const float * w, float eps, float * x, int n_rows, int width, cudaStream_t stream);
+// both at once: x[t] += layernorm(m[t]) * wa, then y[t] = layernorm(x[t]) * wb (the next sublayer's input)
+int launch_layernorm_residual_next(const float * m, const float * wa, const float * wb, float eps, float * x, void * y, int otype, int n_rows, int width,
+                                   cudaStream_t stream);
 // y[t][j] = gelu_tanh(gu[t][j]) * gu[t][ff + j]       gu: [T][2 ff] f32
 int launch_gelu_mul(const float * gu, void * y, int otype, int n_tokens, int ff, cudaStream_t stream);
 // out[r] = first index of the maximum of logits[r][0..n)

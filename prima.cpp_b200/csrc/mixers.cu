@@ -86,6 +86,34 @@ __global__ void __launch_bounds__(256) k_layernorm(const float * __restrict__ x,
     }
 }
 
+// x[t] += layernorm(m[t]) * wa, then y[t] = layernorm(x[t]) * wb: the post-norm + residual of one sublayer and the pre-norm of the next in
+// one pass over the token (every thread re-reads only the elements of x it has written itself)
+template <typename OT>
+__global__ void __launch_bounds__(256) k_layernorm_residual_next(const float * __restrict__ m, const float * __restrict__ wa, const float * __restrict__ wb,
+                                                                 float eps, float * __restrict__ x, OT * __restrict__ y, int width) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const float * in = m + (int64_t) r * width;
+    float * xr = x + (int64_t) r * width;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) s += in[i];
+    const float mean = block_sum(s, red) / (float) width;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float d = in[i] - mean; q = fmaf(d, d, q); }
+    const float inv = 1.f / sqrtf(block_sum(q, red) / (float) width + eps);
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = xr[i] + (in[i] - mean) * inv * wa[i];
+        xr[i] = v;
+        s2 += v;
+    }
+    const float mean2 = block_sum(s2, red) / (float) width;
+    float q2 = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float d = xr[i] - mean2; q2 = fmaf(d, d, q2); }
+    const float inv2 = 1.f / sqrtf(block_sum(q2, red) / (float) width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) put(y, (int64_t) r * width + i, (xr[i] - mean2) * inv2 * wb[i]);
+}
+
 template <typename OT>
 __global__ void k_gelu_mul(const float * __restrict__ gu, OT * __restrict__ y, int n_tokens, int ff) {
     const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
@@ -369,10 +397,10 @@ __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const float *
     }
 }
 
-// decode: one CTA of 16 warps per (head, entry).  Warp w takes cache rows w, w + 16, ...: the lanes split the key's dimensions (coalesced
-// row reads), the score is a warp sum, the running max / sum are uniform over the warp, and every lane accumulates its share of the value
-// dimensions.  The 16 partial softmax states are merged in shared memory.
-constexpr int DEC_WARPS = 16;
+// decode: one CTA of 32 warps per (head, entry).  Warp w takes cache rows 4 w .. 4 w + 3, then 128 further on, ...: the lanes split the key's
+// dimensions (coalesced row reads, four rows in flight), the score is a warp sum, the running max / sum are uniform over the warp, and every lane accumulates its share of the value
+// dimensions.  The 32 partial softmax states are merged in shared memory.
+constexpr int DEC_WARPS = 32, DEC_ROWS = 4;
 template <typename OT, int NV>
 __global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const float * __restrict__ qkvg, const int32_t * __restrict__ slot,
                                                                        const int32_t * __restrict__ off, const int32_t * __restrict__ pos0, AttnParams a,
@@ -398,39 +426,62 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const flo
     for (int c = 0; c < NV; c++) acc[c] = 0.f;
     const int rows_used = min(a.cache_rows, pi + 1);
     const bool vec4 = (D & 3) == 0;
-    for (int r = warp; r < rows_used; r += DEC_WARPS) {
-        // which position does row r hold right now?
-        int p;
-        if (r < keep) p = r;
-        else {
-            const int rr = r - keep, ip = pi - keep;           // ip >= 0 here because r < rows_used <= pi + 1
-            p = keep + ip - ((ip - rr) % ring + ring) % ring;
-            if (p < keep) p = -1;
-        }
-        const bool valid = p >= 0 && p <= pi && (a.window <= 0 || pi - p < a.window || p < a.keep_first);
-        if (!valid) continue;                                   // uniform over the warp
-        const float * kr = kc + (int64_t) r * KD + kvh * D;
-        float s = 0.f;
-        if (vec4) {
-            for (int d = lane * 4; d < D; d += 128) {
-                const float4 kv = *reinterpret_cast<const float4 *>(kr + d);
-                const float4 qv = *reinterpret_cast<const float4 *>(qs + d);
-                s = fmaf(qv.x, kv.x, s); s = fmaf(qv.y, kv.y, s); s = fmaf(qv.z, kv.z, s); s = fmaf(qv.w, kv.w, s);
+    for (int r0 = warp * DEC_ROWS; r0 < rows_used; r0 += DEC_WARPS * DEC_ROWS) {
+        // DEC_ROWS rows per step so that their loads are in flight together; which position does row r hold right now?
+        float sc[DEC_ROWS];
+#pragma unroll
+        for (int j = 0; j < DEC_ROWS; j++) {
+            const int r = r0 + j;
+            int p = -1;
+            if (r < rows_used) {
+                if (r < keep) p = r;
+                else {
+                    const int rr = r - keep, ip = pi - keep;       // ip >= 0 here because r < rows_used <= pi + 1
+                    p = keep + ip - ((ip - rr) % ring + ring) % ring;
+                    if (p < keep) p = -1;
+                }
             }
-        } else {
-            for (int d = lane; d < D; d += 32) s = fmaf(qs[d], kr[d], s);
+            const bool valid = p >= 0 && p <= pi && (a.window <= 0 || pi - p < a.window || p < a.keep_first);   // uniform over the warp
+            float s = 0.f;
+            if (valid) {
+                const float * kr = kc + (int64_t) r * KD + kvh * D;
+                if (vec4) {
+                    for (int d = lane * 4; d < D; d += 128) {
+                        const float4 kv = *reinterpret_cast<const float4 *>(kr + d);
+                        const float4 qv = *reinterpret_cast<const float4 *>(qs + d);
+                        s = fmaf(qv.x, kv.x, s); s = fmaf(qv.y, kv.y, s); s = fmaf(qv.z, kv.z, s); s = fmaf(qv.w, kv.w, s);
+                    }
+                } else {
+                    for (int d = lane; d < D; d += 32) s = fmaf(qs[d], kr[d], s);
+                }
+            }
+            sc[j] = valid ? s : -INFINITY;
         }
-        s = wsum(s);
-        if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
-        const float mn = fmaxf(m, s);
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < DEC_ROWS; j++) {
+            if (sc[j] != -INFINITY) {                               // uniform: validity does not depend on the lane
+                float s = wsum(sc[j]);
+                if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+                sc[j] = s;
+                tmax = fmaxf(tmax, s);
+            }
+        }
+        if (tmax == -INFINITY) continue;
+        const float mn = fmaxf(m, tmax);
         const float corr = m == -INFINITY ? 0.f : expf(m - mn);
-        const float pj = expf(s - mn);
-        l = l * corr + pj;
-        const float * vr = vc + (int64_t) r * VD + kvh * DV;
+        float pj[DEC_ROWS], psum = 0.f;
+#pragma unroll
+        for (int j = 0; j < DEC_ROWS; j++) { pj[j] = sc[j] == -INFINITY ? 0.f : expf(sc[j] - mn); psum += pj[j]; }
+        l = l * corr + psum;
 #pragma unroll
         for (int c = 0; c < NV; c++) {
             const int d = lane + 32 * c;
-            acc[c] = fmaf(pj, d < DV ? vr[d] : 0.f, acc[c] * corr);
+            float v = acc[c] * corr;
+#pragma unroll
+            for (int j = 0; j < DEC_ROWS; j++)
+                if (pj[j] != 0.f && d < DV) v = fmaf(pj[j], vc[(int64_t) (r0 + j) * VD + kvh * DV + d], v);
+            acc[c] = v;
         }
         m = mn;
     }
@@ -677,6 +728,14 @@ int launch_layernorm(const float * x, const int32_t * rows, const float * w, flo
 int launch_layernorm_residual(const float * m, const float * w, float eps, float * x, int n_rows, int width, cudaStream_t st) {
     if (n_rows <= 0) return 0;
     return ck_launch([&] { k_layernorm<float, true><<<n_rows, 256, 0, st>>>(m, nullptr, w, eps, nullptr, x, width); });
+}
+int launch_layernorm_residual_next(const float * m, const float * wa, const float * wb, float eps, float * x, void * y, int otype, int n_rows, int width,
+                                   cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    return ck_launch([&] {
+        if (otype == T_BF16) k_layernorm_residual_next<__nv_bfloat16><<<n_rows, 256, 0, st>>>(m, wa, wb, eps, x, (__nv_bfloat16 *) y, width);
+        else k_layernorm_residual_next<float><<<n_rows, 256, 0, st>>>(m, wa, wb, eps, x, (float *) y, width);
+    });
 }
 int launch_gelu_mul(const float * gu, void * y, int otype, int n_tokens, int ff, cudaStream_t st) {
     const int64_t n = (int64_t) n_tokens * ff;

@@ -253,7 +253,8 @@ def test_far_token_through_the_recurrent_state(pkg, cuda):
     check(got, want[200:], F32_TOL)
 
 
-@pytest.mark.parametrize("variant", ["no_kept_tokens", "window_longer_than_sequence", "window_of_one", "one_head_one_group_one_tap", "wide_values", "no_loop_no_softcap"])
+@pytest.mark.parametrize("variant", ["no_kept_tokens", "window_longer_than_sequence", "window_of_one", "one_head_one_group_one_tap", "wide_values", "no_loop_no_softcap",
+                                     "large_state_odd_dims"])
 def test_other_sizes(pkg, cuda, variant):
     if variant == "no_kept_tokens":
         cfg = config([attn_layer(size=5, keep=0, ff=40), ssm_layer()], width=48)
@@ -266,6 +267,8 @@ def test_other_sizes(pkg, cuda, variant):
                      width=44, vocab=33, loop={"start": 0, "stop": 2, "times": 1})
     elif variant == "wide_values":
         cfg = config([attn_layer(heads=2, kv_heads=1, dim=16, vdim=200, size=6, keep=2), ssm_layer(heads=2, vdim=70, state=40, groups=2, conv=5, norm_groups=5)], width=56)
+    elif variant == "large_state_odd_dims":              # a state too large for the register-resident scan; head sizes that are no multiple of 4
+        cfg = config([ssm_layer(heads=2, vdim=10, state=136, groups=1, conv=3, norm_groups=2), attn_layer(heads=4, kv_heads=2, dim=18, vdim=6, size=8, keep=2)], width=52)
     else:
         cfg = config([attn_layer(softcap=0.0, ff=64), ssm_layer(ff=32)], width=64, logit_scale=1.0)
         del cfg["layers"][0]["mixer"]["softcap"]
