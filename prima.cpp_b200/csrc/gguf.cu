@@ -23,6 +23,7 @@
 #include <vector>
 
 #include "../../include/prima_b200.h"
+#include "arch.h"
 #include "common.cuh"
 
 namespace {
@@ -185,7 +186,8 @@ const GgufTensor * find(const GgufFile & g, const std::string & name) {
 }
 
 int gguf_hparams(const GgufFile & g, int n_ctx, pb200_hparams * hp) {
-    if (g.arch != "llama" && g.arch != "qwen2") return PB200_ENOTSUP;
+    const pb::ArchEntry * arch = pb::arch_find(g.arch.c_str());             // the architecture table decides which graph a container gets
+    if (!arch || arch->family != pb::ARCH_KQUANT) return PB200_ENOTSUP;
     auto key = [&](const char * k) { return g.arch + "." + k; };
     auto geti = [&](const char * k, double def) { auto it = g.num.find(key(k)); return it == g.num.end() ? def : it->second; };
     memset(hp, 0, sizeof *hp);
@@ -205,7 +207,7 @@ int gguf_hparams(const GgufFile & g, int n_ctx, pb200_hparams * hp) {
     const std::string sc = g.str.count(key("rope.scaling.type")) ? g.str.at(key("rope.scaling.type")) : std::string("none");
     hp->rope_freq_scale = (sc == "linear" && factor > 0.0) ? (float) (1.0 / factor) : 1.0f;   // YaRN etc.: not handled by this loader
     hp->rms_eps = (float) geti("attention.layer_norm_rms_epsilon", 1e-5);
-    hp->rope_mode = g.arch == "qwen2" ? 2 : 0;                                             // llama_rope_type (src/llama.cpp): NORM / NEOX
+    hp->rope_mode = arch->rope_mode;                                                       // llama_rope_type (src/llama.cpp): NORM / NEOX
     const GgufTensor * emb = find(g, "token_embd.weight");
     if (!emb || emb->ne[0] != hp->n_embd) return PB200_EINVAL;
     hp->n_vocab = (int32_t) emb->ne[1];

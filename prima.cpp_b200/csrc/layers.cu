@@ -1,8 +1,8 @@
 // prima.cpp_b200/csrc/layers.cu — the engine of the layer-list family (arch.h): a configuration file lists the layers, every layer has
 // a sequence mixer (windowed attention with kept first tokens, or a Mamba-2 state-space mixer) and an optional gated feed-forward,
 // weights are dense f32 / bf16 matrices.  It lives behind the same model object and C ABI as the k-quant transformer engine
-// (engine.cu): pb200_model_set_tensor / _finalize / _free, sequence slots, pb200_decode / pb200_prefill on slot 0, device arg-max —
-// plus the ragged batch step (pb200_batch_step) that the scheduler drives.
+// (engine.cu): pb200_model_set_tensor / _synth / _finalize / _free, sequence slots, device arg-max — and steps through the ragged
+// batch step (pb200_batch_step) that the scheduler drives; the single-sequence entry points of the k-quant family answer PB200_ENOTSUP.
 //
 // State manager: every sequence slot owns one arena of constant size.  Per layer RUN (a layer inside a repeated block runs several
 // times per token and each pass has its own state): attention -> K and V rows (positions below keep_first at their own row, later ones

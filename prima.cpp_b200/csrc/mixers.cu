@@ -179,10 +179,6 @@ __global__ void k_attn_kv_store(const float * __restrict__ qkvg, const int32_t *
 constexpr int AQ = 4;      // queries per CTA (one per warp)
 constexpr int AKT = 32;    // keys per tile
 
-struct AttnAcc {
-    float m = -INFINITY, l = 0.f;
-};
-
 template <int NV>
 __device__ __forceinline__ void attn_tile_update(float score, bool valid, const float * __restrict__ vt, int vdim, int lane, float & m, float & l,
                                                  float (&acc)[NV]) {
