@@ -326,7 +326,7 @@ def test_model_directory_loader_and_missing_tensor(pkg, cuda, tmp_path):
         pkg.Model.from_dir(tmp_path / "unknown", dtype="float32", n_ctx=64)
 
 
-@pytest.mark.parametrize("T,N,K", [(1, 96, 64), (3, 130, 72), (8, 257, 256), (9, 128, 64), (64, 300, 136), (200, 512, 384), (257, 129, 1032), (700, 904, 256)])
+@pytest.mark.parametrize("T,N,K", [(1, 96, 64), (3, 130, 72), (5, 140, 80), (8, 257, 256), (9, 128, 64), (64, 300, 136), (100, 384, 200), (128, 129, 64), (200, 512, 384), (257, 129, 1032), (700, 904, 256)])
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 def test_dense_product_kernels(pkg, lib, cuda, T, N, K, dtype):
     """Every kernel behind the dense product (few-token rows, tiles, tensor cores) against a float64 product of the same operands."""
