@@ -1,13 +1,17 @@
 // prima.cpp_b200/csrc/layers.cu — the engine of the layer-list family (arch.h): a configuration file lists the layers, every layer has
-// a sequence mixer (windowed attention with kept first tokens, or a Mamba-2 state-space mixer) and an optional gated feed-forward,
-// weights are dense f32 / bf16 matrices.  It lives behind the same model object and C ABI as the k-quant transformer engine
+// a sequence mixer (windowed attention with kept first tokens, a Mamba-2 state-space mixer, linear attention with a fixed decay per
+// head, or softmax attention over a low-rank latent) and an optional feed-forward (tanh-GELU gated; clamped gated, dense or a routed
+// mixture of experts), inside one of two layer frames: norms before and after every sublayer (FRAME_SANDWICH), or a grouped RMS norm
+// before it with token shift and a depth average of all layer results (FRAME_PRENORM).  Weights are dense f32 / bf16 matrices.  It lives behind the same model object and C ABI as the k-quant transformer engine
 // (engine.cu): pb200_model_set_tensor / _synth / _finalize / _free, sequence slots, device arg-max — and steps through the ragged
 // batch step (pb200_batch_step) that the scheduler drives; the single-sequence entry points of the k-quant family answer PB200_ENOTSUP.
 //
 // State manager: every sequence slot owns one arena of constant size.  Per layer RUN (a layer inside a repeated block runs several
 // times per token and each pass has its own state): attention -> K and V rows (positions below keep_first at their own row, later ones
-// in a ring as long as the window), Mamba-2 -> the last taps-1 convolution inputs and the fp32 state [heads][state][vdim].  A slot's
-// arena is zeroed when it is handed out, so a reused slot starts like a new one.
+// in a ring as long as the window), Mamba-2 -> the last taps-1 convolution inputs and the fp32 state [heads][state][vdim], decay
+// attention -> the fp32 state [heads][dim][vdim], latent attention -> one row [latent | rotated key part] per position (a layer that
+// reads another layer's latent has none of its own), token shift -> the normed input of the last token.  A slot's arena is zeroed when
+// it is handed out, so a reused slot starts like a new one.
 //
 // Precision: the residual stream, norms, attention scores / weights, recurrent state and everything that feeds the recurrence are
 // fp32 in both compute types; with T_BF16 only the two operands of a dense product are bf16 (fp32 accumulation).
@@ -42,7 +46,9 @@ extern std::atomic<uint64_t> g_launches;
 
 namespace pb {
 
-enum : int { MIX_ATTENTION = 0, MIX_MAMBA2 = 1 };
+enum : int { MIX_ATTENTION = 0, MIX_MAMBA2 = 1, MIX_DECAY = 2, MIX_LATENT = 3 };
+enum : int { FF_GELU = 0, FF_CLAMPED = 1, FF_MOE = 2 };
+enum : int { FRAME_SANDWICH = 0, FRAME_PRENORM = 1 };
 
 struct DenseW {           // row-major [N][K] in the model's compute type
     void * data = nullptr;
@@ -53,6 +59,7 @@ struct VecF {             // small fp32 parameter (norm weights, convolution tap
     float * data = nullptr;
     int64_t n = 0;
     bool filled = false;
+    std::vector<float> preset;   // non-empty: values the configuration fixes (decays, rotation frequencies); no checkpoint tensor fills it
 };
 
 struct LLayer {
@@ -65,12 +72,34 @@ struct LLayer {
     DenseW in;                         // mamba2 input projection  z | x | B | C | dt
     VecF conv_w, conv_b, dt_bias, A_log, D, gnorm;
     DenseW gateup, down;               // feed-forward: fused gate | up
+    int ff_kind = FF_GELU;
+    float ff_limit = 0.f;              // FF_CLAMPED
+    // decay attention (qkvg: fused q | k | v | gate with a gate logit per output element)
+    DecayAttnParams dec;
+    int dec_norm_groups = 1;           // output norm: 1 = all heads together, heads = every head by itself
+    bool dec_norm_weight = false;
+    int dec_gate_act = 0;              // 0 sigmoid, 1 silu
+    VecF decay, onorm;
+    // latent attention (lproj: fused dq | gate | dkv)
+    LatentParams lat;
+    int kv_from = -1;                  // >= 0: the layer whose latent cache this one reads
+    DenseW lproj, uq, uk, uv;
+    VecF dq_norm, dkv_norm, rot_freq;
+    // mixture of experts: e_gateup [experts][2 ff][width], e_down [experts][width][ff]; a shared expert beside them (shared_ff > 0)
+    MoeParams moe;
+    DenseW e_gateup, e_down, s_gateup, s_down;
+    VecF router, router_b;
+    int shared_ff = 0;
+    float shared_limit = 0.f;
+    // FRAME_PRENORM
+    VecF shift, dwa;
 };
 
 struct LRun {
     int layer = 0;
     int pass = -1;            // >= 0: this run opens pass `pass` of the repeated block (input mix + step vector come first)
-    int64_t state_off = 0;    // floats from the slot's arena base
+    int64_t state_off = 0;    // floats from the slot's arena base (a latent layer that reads another layer's cache: that layer's offset)
+    int64_t shift_off = -1;   // token-shift state [width]
 };
 
 // where a checkpoint tensor goes
@@ -85,6 +114,8 @@ struct TensorPlace {
 struct LayerList {
     const ArchEntry * arch = nullptr;
     int ctype = T_BF16;       // compute type: operand type of the dense products
+    int frame = FRAME_SANDWICH;
+    int norm_groups = 1;      // FRAME_PRENORM: groups of the RMS norm
     int width = 0, vocab = 0;
     float eps = 1e-6f, logit_scale = 1.f;
     std::vector<LLayer> layers;
@@ -105,6 +136,12 @@ struct LayerList {
     int capT = 0, capW = 0;
     float *x = nullptr, *x0 = nullptr, *xalt = nullptr, *big = nullptr, *msub = nullptr, *xbc = nullptr, *yssm = nullptr, *logits = nullptr;
     void *act = nullptr, *act2 = nullptr, *actw = nullptr;
+    // FRAME_PRENORM and its mixers: results of all layers [layers + 1][capT][width]; further fp32 and operand-type scratch
+    float *hist = nullptr, *big2 = nullptr, *big3 = nullptr, *big4 = nullptr, *krb = nullptr;
+    // mixture of experts: pairs (token, choice)
+    int32_t *moe_idx = nullptr, *moe_perm = nullptr, *moe_row_of = nullptr, *moe_count = nullptr, *moe_start = nullptr, *moe_count_host = nullptr;
+    float *moe_wt = nullptr, *moe_gu = nullptr, *moe_ds = nullptr;
+    void *moe_y = nullptr, *moe_hs = nullptr;
     int32_t *meta_dev = nullptr, *meta_host = nullptr, *greedy_dev = nullptr, *greedy_host = nullptr;
     float * logits_host = nullptr;
     size_t meta_cap = 0, logits_host_cap = 0;
@@ -256,10 +293,208 @@ static bool vamidra_resolve(LayerList & ll, const std::string & name, TensorPlac
     return false;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Mumizen: configuration keys and tensor names.  Pre-norm layers (RMS norm in groups), token shift on the mixer's input, depth average
+// after every layer; mixers "lightning" / "retention" (decay attention) and "latent_attention"; clamped gated feed-forward, dense or "moe".
+static int clamped_ff_config(const Json & jm, int & ff, float & limit, std::string & err) {
+    ff = (int) jm.integer("ff", 0);
+    limit = (float) jm.number("limit", 0.0);
+    if (ff <= 0 || !(limit > 0.f)) { err = "feed-forward size / limit"; return PB200_EINVAL; }
+    return 0;
+}
+// rotation frequencies with the long-context blend: below turn-count `fast` per original context a pair keeps its frequency, above
+// `slow` it is divided by `factor`, linear in the pair index between; cos and sin then carry 0.1 ln(factor) + 1
+static void rotary_table(const Json & rot, int dims, std::vector<float> & freq, float & mag) {
+    const double base = rot.number("base", 10000.0);
+    const int half = dims / 2;
+    freq.assign((size_t) std::max(half, 1), 0.f);
+    mag = 1.f;
+    const Json * sc = rot.get("scaling");
+    const bool scaled = sc && sc->kind == Json::OBJ;
+    double lo = 0, hi = 0, factor = 1;
+    if (scaled) {
+        factor = sc->number("factor", 1.0);
+        const double orig = sc->number("original", 1.0), fast = sc->number("fast", 32.0), slow = sc->number("slow", 1.0);
+        auto turn_dim = [&](double turns) { return dims * std::log(orig / (2.0 * M_PI * turns)) / (2.0 * std::log(base)); };
+        lo = std::max(std::floor(turn_dim(fast)), 0.0);
+        hi = std::min(std::ceil(turn_dim(slow)), (double) dims - 1.0);
+        mag = (float) (0.1 * std::log(factor) + 1.0);
+    }
+    for (int i = 0; i < half; i++) {
+        const double f = std::pow(base, -2.0 * i / dims);
+        double v = f;
+        if (scaled) {
+            const double ramp = std::min(1.0, std::max(0.0, (i - lo) / std::max(hi - lo, 0.001)));
+            v = f / factor * ramp + f * (1.0 - ramp);
+        }
+        freq[(size_t) i] = (float) v;
+    }
+}
+
+static int mumizen_configure(const Json & cfg, LayerList & ll, std::string & err) {
+    ll.frame = FRAME_PRENORM;
+    ll.width = (int) cfg.integer("width", 0);
+    ll.vocab = (int) cfg.integer("vocab", 0);
+    ll.logit_scale = 1.f;
+    ll.norm_groups = 1;
+    if (const Json * nrm = cfg.get("norm")) { ll.eps = (float) nrm->number("eps", 1e-6); ll.norm_groups = (int) nrm->integer("groups", 1); }
+    const Json * layers = cfg.get("layers");
+    if (ll.width <= 0 || ll.vocab <= 0 || !layers || layers->kind != Json::ARR || layers->arr.empty()) { err = "width, vocab and layers are required"; return PB200_EINVAL; }
+    if (ll.norm_groups <= 0 || ll.norm_groups > 64 || ll.width % ll.norm_groups) { err = "norm groups"; return PB200_EINVAL; }
+    for (const Json & jl : layers->arr) {
+        LLayer L;
+        const std::string type = jl.string("type");
+        const Json * mx = jl.get("mixer");
+        if (!mx || mx->kind != Json::OBJ) { err = "layer without mixer"; return PB200_EINVAL; }
+        const int il = (int) ll.layers.size();
+        if (type == "lightning" || type == "retention") {
+            L.kind = MIX_DECAY;
+            DecayAttnParams & d = L.dec;
+            d.heads = (int) mx->integer("heads", 0);
+            d.dim = (int) mx->integer("dim", 0);
+            d.vdim = (int) mx->integer("vdim", d.dim);
+            const Json * dc = mx->get("decay");
+            if (d.heads <= 0 || d.dim <= 0 || d.vdim <= 0 || !dc || dc->kind != Json::ARR || (int) dc->arr.size() != d.heads) { err = type + " sizes / decay"; return PB200_EINVAL; }
+            for (const Json & v : dc->arr) L.decay.preset.push_back((float) v.num);
+            if (type == "lightning") {   // SiLU on q, k, v; all heads normed together with a weight; sigmoid gate
+                d.act = 1; d.k_scale = 1.f;
+                L.dec_norm_groups = 1; L.dec_norm_weight = true; L.dec_gate_act = 0;
+            } else {                     // plain q, k, v with k / sqrt(dim); every head by its own root mean square, no weight; SiLU gate
+                d.act = 0; d.k_scale = (float) (1.0 / std::sqrt((double) d.dim));
+                L.dec_norm_groups = d.heads; L.dec_norm_weight = false; L.dec_gate_act = 1;
+            }
+        } else if (type == "latent_attention") {
+            L.kind = MIX_LATENT;
+            LatentParams & a = L.lat;
+            a.heads = (int) mx->integer("heads", 0);
+            a.dim = (int) mx->integer("dim", 0);
+            a.rot_dim = (int) mx->integer("rot_dim", 0);
+            a.vdim = (int) mx->integer("vdim", a.dim);
+            a.kv_rank = (int) mx->integer("kv_rank", 0);
+            a.q_rank = (int) mx->integer("q_rank", 0);
+            a.scale = (float) mx->number("scale", a.dim + a.rot_dim > 0 ? 1.0 / std::sqrt((double) (a.dim + a.rot_dim)) : 1.0);
+            a.rot_dims = 0;
+            const Json * rot = mx->get("rot");
+            if (rot && rot->kind == Json::OBJ) {
+                a.rot_dims = (int) rot->integer("dims", a.rot_dim);
+                if (a.rot_dims < 0 || a.rot_dims > a.rot_dim || a.rot_dims % 2) { err = "rotated dimensions"; return PB200_EINVAL; }
+                rotary_table(*rot, a.rot_dims, L.rot_freq.preset, a.rot_mag);
+            } else {
+                L.rot_freq.preset.assign(1, 0.f);
+            }
+            const Json * from = mx->get("kv_from");
+            a.own_kv = 1;
+            if (from && from->kind == Json::NUM) {
+                L.kv_from = (int) from->num;
+                a.own_kv = 0;
+                if (L.kv_from < 0 || L.kv_from >= il) { err = "kv_from must name an earlier layer"; return PB200_EINVAL; }
+                const LLayer & S = ll.layers[(size_t) L.kv_from];
+                if (S.kind != MIX_LATENT || !S.lat.own_kv || S.lat.kv_rank != a.kv_rank || S.lat.rot_dim != a.rot_dim) { err = "kv_from: the named layer has no latent cache of this shape"; return PB200_EINVAL; }
+            }
+            if (a.heads <= 0 || a.dim < 0 || a.rot_dim < 0 || a.dim + a.rot_dim <= 0 || a.vdim <= 0 || a.kv_rank <= 0 || a.q_rank <= 0 || a.kv_rank > 512 ||
+                a.vdim > 512) { err = "latent attention sizes"; return PB200_EINVAL; }
+        } else {
+            err = "unknown layer type '" + type + "'";
+            return PB200_ENOTSUP;
+        }
+        const Json * mlp = jl.get("mlp");
+        if (mlp && mlp->kind == Json::OBJ) {
+            const std::string kind = mlp->string("kind", "dense");
+            if (kind == "dense") {
+                L.ff_kind = FF_CLAMPED;
+                int rc = clamped_ff_config(*mlp, L.ff, L.ff_limit, err);
+                if (rc) return rc;
+            } else if (kind == "moe") {
+                L.ff_kind = FF_MOE;
+                const Json * ex = mlp->get("expert"), * ro = mlp->get("router"), * sh = mlp->get("shared");
+                if (!ex || ex->kind != Json::OBJ || !ro || ro->kind != Json::OBJ) { err = "moe needs expert and router"; return PB200_EINVAL; }
+                int rc = clamped_ff_config(*ex, L.moe.ff, L.moe.limit, err);
+                if (rc) return rc;
+                L.ff = L.moe.ff;
+                L.moe.experts = (int) ro->integer("experts", 0);
+                L.moe.top = (int) ro->integer("top", 0);
+                if (L.moe.experts <= 0 || L.moe.top <= 0 || L.moe.top > L.moe.experts || L.moe.top > 32 || L.moe.experts > 4096) { err = "router sizes"; return PB200_EINVAL; }
+                if (sh && sh->kind == Json::OBJ) {
+                    rc = clamped_ff_config(*sh, L.shared_ff, L.shared_limit, err);
+                    if (rc) return rc;
+                }
+            } else {
+                err = "unknown feed-forward kind '" + kind + "'";
+                return PB200_ENOTSUP;
+            }
+        }
+        ll.layers.push_back(std::move(L));
+    }
+    for (int i = 0; i < (int) ll.layers.size(); i++) {
+        LRun r;
+        r.layer = i;
+        ll.runs.push_back(r);
+    }
+    return 0;
+}
+
+static bool mumizen_resolve(LayerList & ll, const std::string & name, TensorPlace & o) {
+    const int64_t W = ll.width;
+    auto mat = [&](DenseW & m, int64_t row0, int64_t rows, int64_t cols, int part) { o.mat = &m; o.row0 = row0; o.rows = rows; o.cols = cols; o.part = part; return true; };
+    auto vec = [&](VecF & v, int64_t n) { o.vec = &v; o.n = n; return true; };
+    if (name == "embed") return mat(ll.embed, 0, ll.vocab, W, 0);
+    if (name == "head") return mat(ll.head, 0, ll.vocab, W, 0);
+    if (name == "final.norm") return vec(ll.final_norm, W);
+    int il = -1, used = 0;
+    if (sscanf(name.c_str(), "l%d.%n", &il, &used) != 1 || used <= 0 || il < 0 || il >= (int) ll.layers.size()) return false;
+    LLayer & L = ll.layers[(size_t) il];
+    const std::string w = name.substr((size_t) used);
+    if (w == "norm1") return vec(L.norm1, W);
+    if (w == "shift") return vec(L.shift, W);
+    if (w == "dwa") return vec(L.dwa, il + 2);
+    // a clamped gated unit `pre`gate / up / down inside fused matrices: gate | up rows at gu_row0, down rows at d_row0
+    auto glu = [&](const std::string & leaf, DenseW & gu, DenseW & dn, int64_t ff, int64_t gu_row0, int64_t d_row0, int part0) {
+        if (leaf == "gate") return mat(gu, gu_row0, ff, W, part0);
+        if (leaf == "up") return mat(gu, gu_row0 + ff, ff, W, part0 + 1);
+        if (leaf == "down") return mat(dn, d_row0, W, ff, part0 / 2);
+        return false;
+    };
+    if (L.ff > 0 && w == "norm2") return vec(L.norm2, W);
+    if (L.ff > 0 && w.compare(0, 4, "mlp.") == 0) {
+        const std::string f = w.substr(4);
+        if (L.ff_kind == FF_CLAMPED) return glu(f, L.gateup, L.down, L.ff, 0, 0, 0);
+        if (f == "router") { o.vec = &L.router; o.n = (int64_t) L.moe.experts * W; return true; }
+        if (f == "router.b") return vec(L.router_b, L.moe.experts);
+        if (f.compare(0, 7, "shared.") == 0) return L.shared_ff > 0 && glu(f.substr(7), L.s_gateup, L.s_down, L.shared_ff, 0, 0, 0);
+        int e = -1, u2 = 0;
+        if (sscanf(f.c_str(), "e%d.%n", &e, &u2) == 1 && u2 > 0 && e >= 0 && e < L.moe.experts)
+            return glu(f.substr((size_t) u2), L.e_gateup, L.e_down, L.moe.ff, (int64_t) e * 2 * L.moe.ff, (int64_t) e * W, 2 * e);
+        return false;
+    }
+    if (L.kind == MIX_DECAY) {
+        const int64_t QD = (int64_t) L.dec.heads * L.dec.dim, VD = (int64_t) L.dec.heads * L.dec.vdim;
+        if (w == "mix.q") return mat(L.qkvg, 0, QD, W, 0);
+        if (w == "mix.k") return mat(L.qkvg, QD, QD, W, 1);
+        if (w == "mix.v") return mat(L.qkvg, 2 * QD, VD, W, 2);
+        if (w == "mix.g") return mat(L.qkvg, 2 * QD + VD, VD, W, 3);
+        if (w == "mix.o") return mat(L.out, 0, W, VD, 0);
+        if (w == "mix.norm") return L.dec_norm_weight && vec(L.onorm, VD);
+    } else if (L.kind == MIX_LATENT) {
+        const LatentParams & a = L.lat;
+        const int64_t VD = (int64_t) a.heads * a.vdim;
+        if (w == "mix.dq") return mat(L.lproj, 0, a.q_rank, W, 0);
+        if (w == "mix.g") return mat(L.lproj, a.q_rank, VD, W, 1);
+        if (w == "mix.dkv") return a.own_kv && mat(L.lproj, a.q_rank + VD, a.kv_rank + a.rot_dim, W, 2);
+        if (w == "mix.dq.norm") return vec(L.dq_norm, a.q_rank);
+        if (w == "mix.dkv.norm") return a.own_kv && vec(L.dkv_norm, a.kv_rank);
+        if (w == "mix.uq") return mat(L.uq, 0, (int64_t) a.heads * (a.dim + a.rot_dim), a.q_rank, 0);
+        if (w == "mix.uk") return mat(L.uk, 0, (int64_t) a.heads * a.dim, a.kv_rank, 0);
+        if (w == "mix.uv") return mat(L.uv, 0, VD, a.kv_rank, 0);
+        if (w == "mix.o") return mat(L.out, 0, W, VD, 0);
+    }
+    return false;
+}
+
 static const ArchEntry g_archs[] = {
     {"llama", ARCH_KQUANT, 0, nullptr, nullptr},
     {"qwen2", ARCH_KQUANT, 2, nullptr, nullptr},
     {"Vamidra", ARCH_LAYERS, 0, vamidra_configure, vamidra_resolve},
+    {"Mumizen", ARCH_LAYERS, 0, mumizen_configure, mumizen_resolve},
 };
 int arch_count() { return (int) (sizeof(g_archs) / sizeof(g_archs[0])); }
 const ArchEntry * arch_at(int i) { return (i >= 0 && i < arch_count()) ? &g_archs[i] : nullptr; }
@@ -281,22 +516,50 @@ static void for_each_param(LayerList & ll, FM && fm, FV && fv) {
     fm(ll.head, (int64_t) ll.vocab, W, 1);
     fv(ll.final_norm, W, 0);
     if (ll.loop_times > 0) { fm(ll.loop_in, W, 2 * W, 1); fv(ll.loop_step, (int64_t) ll.loop_times * W, 1); }
+    int il = 0;
     for (LLayer & L : ll.layers) {
-        fv(L.norm1, W, 0); fv(L.norm1b, W, 0);
+        fv(L.norm1, W, 0);
+        if (ll.frame == FRAME_SANDWICH) fv(L.norm1b, W, 0);
+        else { fv(L.shift, W, 5); fv(L.dwa, il + 2, 6); }
+        il++;
         if (L.kind == MIX_ATTENTION) {
             fm(L.qkvg, attn_qkvg_cols(L.att), W, 4);
             fm(L.out, W, (int64_t) L.att.heads * L.att.vdim, 1);
-        } else {
+        } else if (L.kind == MIX_MAMBA2) {
             const Mamba2Params & p = L.ssm;
             fm(L.in, mamba2_in_cols(p), W, 1);
             fv(L.conv_w, (int64_t) mamba2_conv_channels(p) * p.conv, 2); fv(L.conv_b, mamba2_conv_channels(p), 1);
             fv(L.dt_bias, p.heads, 3); fv(L.A_log, p.heads, 4); fv(L.D, p.heads, 0); fv(L.gnorm, mamba2_inner(p), 0);
             fm(L.out, W, mamba2_inner(p), 1);
+        } else if (L.kind == MIX_DECAY) {
+            const int64_t QD = (int64_t) L.dec.heads * L.dec.dim, VD = (int64_t) L.dec.heads * L.dec.vdim;
+            fm(L.qkvg, 2 * QD + 2 * VD, W, 4);
+            fm(L.out, W, VD, 1);
+            fv(L.decay, L.dec.heads, 0);
+            if (L.dec_norm_weight) fv(L.onorm, VD, 0);
+        } else {
+            const LatentParams & a = L.lat;
+            fm(L.lproj, latent_proj_cols(a), W, a.own_kv ? 3 : 2);
+            fv(L.dq_norm, a.q_rank, 0);
+            if (a.own_kv) fv(L.dkv_norm, a.kv_rank, 0);
+            fv(L.rot_freq, (int64_t) L.rot_freq.preset.size(), 0);
+            fm(L.uq, (int64_t) a.heads * (a.dim + a.rot_dim), a.q_rank, 1);
+            fm(L.uk, (int64_t) a.heads * a.dim, a.kv_rank, 1);
+            fm(L.uv, (int64_t) a.heads * a.vdim, a.kv_rank, 1);
+            fm(L.out, W, (int64_t) a.heads * a.vdim, 1);
         }
         if (L.ff > 0) {
-            fv(L.norm2, W, 0); fv(L.norm2b, W, 0);
-            fm(L.gateup, 2 * (int64_t) L.ff, W, 2);
-            fm(L.down, W, L.ff, 1);
+            fv(L.norm2, W, 0);
+            if (ll.frame == FRAME_SANDWICH) fv(L.norm2b, W, 0);
+            if (L.ff_kind == FF_MOE) {
+                fm(L.e_gateup, (int64_t) L.moe.experts * 2 * L.moe.ff, W, 2 * L.moe.experts);
+                fm(L.e_down, (int64_t) L.moe.experts * W, L.moe.ff, L.moe.experts);
+                fv(L.router, (int64_t) L.moe.experts * W, 7); fv(L.router_b, L.moe.experts, 1);
+                if (L.shared_ff > 0) { fm(L.s_gateup, 2 * (int64_t) L.shared_ff, W, 2); fm(L.s_down, W, L.shared_ff, 1); }
+            } else {
+                fm(L.gateup, 2 * (int64_t) L.ff, W, 2);
+                fm(L.down, W, L.ff, 1);
+            }
         }
     }
 }
@@ -319,6 +582,10 @@ static int ll_alloc_params(pb200_model * m) {
             v.n = n; v.filled = false;
             rc = m->alloc((void **) &v.data, (size_t) n * 4);
             bytes += n * 4;
+            if (!rc && !v.preset.empty()) {   // fixed by the configuration
+                rc = (int) cudaMemcpy(v.data, v.preset.data(), (size_t) n * 4, cudaMemcpyHostToDevice);
+                v.filled = true;
+            }
         });
     ll.weight_bytes = bytes;
     return rc;
@@ -407,10 +674,11 @@ int ll_synth(pb200_model * m, uint64_t seed) {
             rc = (int) cudaGetLastError();
             std::fill(d.filled.begin(), d.filled.end(), 1);
         },
-        [&](VecF & v, int64_t n, int kind) {   // kind 0: around one, 1: around zero, 2: convolution taps, 3: dt bias, 4: log of the decay rate
-            if (rc) return;
-            const float base = kind == 0 ? 1.f : kind == 3 ? -2.f : kind == 4 ? 0.5f : 0.f;
-            const float hr = kind == 0 ? 0.05f : kind == 1 ? 0.02f : kind == 2 ? 0.5f : 1.f;
+        [&](VecF & v, int64_t n, int kind) {   // kind 0: around one, 1: around zero, 2: convolution taps, 3: dt bias, 4: log of the decay rate,
+            if (rc || !v.preset.empty()) return;   // 5: shift blend in [0, 1], 6: depth-average weights around 1 / n, 7: router rows
+            const float base = kind == 0 ? 1.f : kind == 3 ? -2.f : kind == 4 ? 0.5f : kind == 5 ? 0.5f : kind == 6 ? 1.f / (float) n : 0.f;
+            const float hr = kind == 0 ? 0.05f : kind == 1 ? 0.02f : kind == 2 ? 0.5f : kind == 5 ? 0.5f : kind == 6 ? 0.5f / (float) n
+                             : kind == 7 ? 1.7320508f / sqrtf((float) ll.width) : 1.f;
             k_fill_uniform<float><<<(unsigned) ((n + 255) / 256), 256, 0, m->stream>>>(v.data, n, base, hr, ++sd);
             rc = (int) cudaGetLastError();
             v.filled = true;
@@ -433,8 +701,16 @@ int ll_finalize(pb200_model * m) {
     ll.ctx_limited = false;
     for (LRun & r : ll.runs) {
         LLayer & L = ll.layers[(size_t) r.layer];
+        if (ll.frame == FRAME_PRENORM) { r.shift_off = off; off += ll.width; off = (off + 3) / 4 * 4; }
         r.state_off = off;
-        if (L.kind == MIX_ATTENTION) {
+        if (L.kind == MIX_DECAY) {
+            off += (int64_t) L.dec.heads * L.dec.dim * L.dec.vdim;
+        } else if (L.kind == MIX_LATENT) {
+            L.lat.cache_rows = ll.n_ctx;
+            ll.ctx_limited = true;
+            if (L.lat.own_kv) off += (int64_t) ll.n_ctx * latent_row(L.lat);
+            else r.state_off = ll.runs[(size_t) L.kv_from].state_off;   // FRAME_PRENORM: run i is layer i
+        } else if (L.kind == MIX_ATTENTION) {
             L.att.cache_rows = attn_cache_rows(L.att.window, L.att.keep_first, ll.n_ctx);
             if (L.att.cache_rows >= ll.n_ctx) ll.ctx_limited = true;
             off += (int64_t) L.att.cache_rows * L.att.kv_heads * (L.att.dim + L.att.vdim);
@@ -467,6 +743,7 @@ void ll_free(pb200_model * m) {
     if (ll->meta_host) cudaFreeHost(ll->meta_host);
     if (ll->greedy_host) cudaFreeHost(ll->greedy_host);
     if (ll->logits_host) cudaFreeHost(ll->logits_host);
+    if (ll->moe_count_host) cudaFreeHost(ll->moe_count_host);
     if (ll->tap) cudaFree(ll->tap);
     for (cudaEvent_t e : ll->prof_ev) cudaEventDestroy(e);
     delete ll;
@@ -515,19 +792,44 @@ static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
         ll.scratch.clear();
         const int cT = std::max(T, ll.capT), cW = std::max(nW, ll.capW);
         ll.capT = ll.capW = 0;
-        int64_t maxact = ll.width, maxbig = ll.width, maxch = 1, maxinner = 1;
+        int64_t maxact = ll.width, maxact2 = ll.width, maxbig = ll.width, maxch = 1, maxinner = 1, maxb2 = 0, maxb3 = 0, maxb4 = 0, maxkr = 0;
+        int64_t moe_top = 0, moe_topff = 0, moe_e = 0;
         for (const LLayer & L : ll.layers) {
             if (L.kind == MIX_ATTENTION) {
                 maxact = std::max<int64_t>(maxact, (int64_t) L.att.heads * L.att.vdim);
                 maxbig = std::max<int64_t>(maxbig, attn_qkvg_cols(L.att));
-            } else {
+            } else if (L.kind == MIX_MAMBA2) {
                 maxact = std::max<int64_t>(maxact, mamba2_inner(L.ssm));
                 maxbig = std::max<int64_t>(maxbig, mamba2_in_cols(L.ssm));
                 maxch = std::max<int64_t>(maxch, mamba2_conv_channels(L.ssm));
                 maxinner = std::max<int64_t>(maxinner, mamba2_inner(L.ssm));
+            } else if (L.kind == MIX_DECAY) {
+                const int64_t QD = (int64_t) L.dec.heads * L.dec.dim, VD = (int64_t) L.dec.heads * L.dec.vdim;
+                maxact = std::max(maxact, VD);
+                maxbig = std::max(maxbig, 2 * QD + 2 * VD);
+                maxinner = std::max(maxinner, VD);
+            } else {
+                const LatentParams & a = L.lat;
+                const int64_t H = a.heads;
+                maxact = std::max(maxact, H * a.vdim);
+                maxact2 = std::max<int64_t>(maxact2, std::max(a.q_rank, a.kv_rank));
+                maxbig = std::max<int64_t>(maxbig, latent_proj_cols(a));
+                maxb2 = std::max(maxb2, H * (a.dim + a.rot_dim));
+                maxb3 = std::max(maxb3, std::max(H * a.dim, H * latent_row(a)));
+                maxb4 = std::max(maxb4, std::max(H * a.vdim, H * a.kv_rank));
+                maxkr = std::max<int64_t>(maxkr, a.rot_dim);
             }
-            maxact = std::max<int64_t>(maxact, L.ff);
-            maxbig = std::max<int64_t>(maxbig, 2 * (int64_t) L.ff);
+            if (L.ff_kind == FF_MOE && L.ff > 0) {
+                maxact2 = std::max<int64_t>(maxact2, L.shared_ff);
+                maxbig = std::max<int64_t>(maxbig, 2 * (int64_t) L.shared_ff);
+                moe_top = std::max<int64_t>(moe_top, L.moe.top);
+                moe_topff = std::max<int64_t>(moe_topff, (int64_t) L.moe.top * L.moe.ff);
+                moe_e = std::max<int64_t>(moe_e, L.moe.experts);
+            } else {
+                maxact = std::max<int64_t>(maxact, L.ff);
+                maxact2 = std::max<int64_t>(maxact2, L.ff);
+                maxbig = std::max<int64_t>(maxbig, 2 * (int64_t) L.ff);
+            }
         }
         auto grab = [&](void ** p, size_t bytes) -> int {
             cudaError_t e = cudaMalloc(p, (bytes + 255) / 256 * 256 + 256);
@@ -542,7 +844,21 @@ static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
         CK(grab((void **) &ll.xbc, t * (size_t) maxch * 4));
         CK(grab((void **) &ll.yssm, t * (size_t) maxinner * 4));
         CK(grab(&ll.act, t * (size_t) maxact * es));
-        CK(grab(&ll.act2, t * W * es));
+        CK(grab(&ll.act2, t * (size_t) maxact2 * es));
+        if (ll.frame == FRAME_PRENORM) CK(grab((void **) &ll.hist, (ll.layers.size() + 1) * t * W * 4));
+        if (maxb2) {
+            CK(grab((void **) &ll.big2, t * (size_t) maxb2 * 4)); CK(grab((void **) &ll.big3, t * (size_t) maxb3 * 4));
+            CK(grab((void **) &ll.big4, t * (size_t) maxb4 * 4)); CK(grab((void **) &ll.krb, t * (size_t) std::max<int64_t>(maxkr, 1) * 4));
+        }
+        if (moe_top) {
+            const size_t pairs = t * (size_t) moe_top;
+            CK(grab((void **) &ll.moe_idx, pairs * 4)); CK(grab((void **) &ll.moe_wt, pairs * 4));
+            CK(grab((void **) &ll.moe_perm, pairs * 4)); CK(grab((void **) &ll.moe_row_of, pairs * 4));
+            CK(grab((void **) &ll.moe_count, (size_t) moe_e * 4)); CK(grab((void **) &ll.moe_start, (size_t) moe_e * 4));
+            CK(grab(&ll.moe_y, t * (size_t) moe_topff * es)); CK(grab(&ll.moe_hs, pairs * W * es));
+            CK(grab((void **) &ll.moe_gu, t * (size_t) moe_topff * 2 * 4)); CK(grab((void **) &ll.moe_ds, pairs * W * 4));
+            if (!ll.moe_count_host) CK(cudaMallocHost((void **) &ll.moe_count_host, (size_t) 2 * 4096 * 4));
+        }
         CK(grab(&ll.actw, (size_t) cW * W * es));
         CK(grab((void **) &ll.logits, (size_t) cW * (size_t) ll.vocab * 4));
         CK(grab((void **) &ll.greedy_dev, (size_t) cW * 4));
@@ -587,27 +903,212 @@ static int prof_mark(pb200_model * m, int cat) {   // an event before the launch
 }
 #define CAT(c) CK(prof_mark(m, c))
 
+static int tap_prepare(pb200_model * m, int T) {
+    LayerList & ll = *m->ll;
+    if (!ll.tap_on) return 0;
+    const int64_t need = (int64_t) ll.runs.size() * T * ll.width;
+    if (need > ll.tap_cap) {
+        CK(cudaStreamSynchronize(m->stream));
+        if (ll.tap) cudaFree(ll.tap);
+        ll.tap = nullptr; ll.tap_cap = 0;
+        CK(cudaMalloc((void **) &ll.tap, (size_t) need * 4));
+        ll.tap_cap = need;
+    }
+    ll.tap_floats = need;
+    ll.tap_T = T;
+    return 0;
+}
+
+// ---- mixers: out[t] = (resid ? resid[t] : 0) + mixer(ll.act[t]); ll.act holds the mixer's input in the operand type ----
+static int mix_attention(pb200_model * m, const BatchView & b, bool prefill, const LRun & r, LLayer & L, const float * resid, float * out) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
+    const AttnParams & a = L.att;
+    const int C = attn_qkvg_cols(a);
+    float * sbase = ll.state + r.state_off;
+    CAT(CAT_DENSE);
+    CK(launch_dense(ct, ll.act, W, L.qkvg.data, W, ll.big, C, T, C, W, nullptr, nullptr, 0, 1.f, st));
+    float * kc = sbase, * vc = sbase + (int64_t) a.cache_rows * a.kv_heads * a.dim;
+    CAT(CAT_ATTN);
+    CK(launch_attn_kv_store(ll.big, b, a, kc, vc, ll.slot_floats, st));
+    if (prefill) CK(launch_attn_window_prefill(ll.big, b, a, ll.act, ct, st));
+    else CK(launch_attn_window_decode(ll.big, b, a, kc, vc, ll.slot_floats, ll.act, ct, st));
+    CAT(CAT_DENSE);
+    return launch_dense(ct, ll.act, (int64_t) a.heads * a.vdim, L.out.data, (int64_t) a.heads * a.vdim, out, W, T, W, a.heads * a.vdim, nullptr, resid, W, 1.f, st);
+}
+static int mix_mamba2(pb200_model * m, const BatchView & b, const LRun & r, LLayer & L, const float * resid, float * out) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
+    const Mamba2Params & p = L.ssm;
+    const int U = mamba2_in_cols(p), inner = mamba2_inner(p);
+    float * sbase = ll.state + r.state_off;
+    CAT(CAT_DENSE);
+    CK(launch_dense(ct, ll.act, W, L.in.data, W, ll.big, U, T, U, W, nullptr, nullptr, 0, 1.f, st));
+    float * cs = sbase, * ss = sbase + (int64_t) (p.conv - 1) * mamba2_conv_channels(p);
+    CAT(CAT_CONV);
+    CK(launch_mamba2_conv(ll.big, b, p, L.conv_w.data, L.conv_b.data, cs, ll.slot_floats, ll.xbc, st));
+    CAT(CAT_SCAN);
+    CK(launch_mamba2_scan(ll.big, ll.xbc, b, p, L.dt_bias.data, L.A_log.data, L.D.data, ss, ll.slot_floats, ll.yssm, st));
+    CAT(CAT_NORM);
+    CK(launch_mamba2_gate_norm(ll.yssm, ll.big, p, L.gnorm.data, ll.eps, ll.act, ct, T, st));
+    CAT(CAT_DENSE);
+    return launch_dense(ct, ll.act, inner, L.out.data, inner, out, W, T, W, inner, nullptr, resid, W, 1.f, st);
+}
+static int mix_decay(pb200_model * m, const BatchView & b, const LRun & r, LLayer & L, const float * resid, float * out) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
+    const DecayAttnParams & d = L.dec;
+    const int QD = d.heads * d.dim, VD = d.heads * d.vdim, C = 2 * QD + 2 * VD;
+    CAT(CAT_DENSE);
+    CK(launch_dense(ct, ll.act, W, L.qkvg.data, W, ll.big, C, T, C, W, nullptr, nullptr, 0, 1.f, st));
+    CAT(CAT_SCAN);
+    CK(launch_decay_attn(ll.big, C, 0, QD, 2 * QD, b, d, L.decay.data, ll.state + r.state_off, ll.slot_floats, ll.yssm, st));
+    CAT(CAT_NORM);
+    CK(launch_norm_gate(ll.yssm, ll.big + 2 * QD + VD, C, L.dec_norm_groups, L.dec_norm_weight ? L.onorm.data : nullptr, L.dec_gate_act, ll.eps, ll.act, ct, T, VD, st));
+    CAT(CAT_DENSE);
+    return launch_dense(ct, ll.act, VD, L.out.data, VD, out, W, T, W, VD, nullptr, resid, W, 1.f, st);
+}
+static int mix_latent(pb200_model * m, const BatchView & b, bool prefill, const LRun & r, LLayer & L, const float * resid, float * out) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
+    const LatentParams & a = L.lat;
+    const int H = a.heads, C = latent_proj_cols(a), DQ = a.dim + a.rot_dim, VD = H * a.vdim, R = a.kv_rank, RW = latent_row(a);
+    float * cache = ll.state + r.state_off;       // this layer's rows, or those of the layer it reads
+    const float * gate = ll.big + a.q_rank;
+    CAT(CAT_DENSE);
+    CK(launch_dense(ct, ll.act, W, L.lproj.data, W, ll.big, C, T, C, W, nullptr, nullptr, 0, 1.f, st));
+    CAT(CAT_ATTN);
+    CK(launch_latent_prep(ll.big, b, a, L.dq_norm.data, L.dkv_norm.data, L.rot_freq.data, ll.eps, ll.act2, ct, cache, ll.slot_floats, st));
+    CAT(CAT_DENSE);
+    CK(launch_dense(ct, ll.act2, a.q_rank, L.uq.data, a.q_rank, ll.big2, (int64_t) H * DQ, T, H * DQ, a.q_rank, nullptr, nullptr, 0, 1.f, st));
+    CAT(CAT_ATTN);
+    CK(launch_latent_rope_q(ll.big2, b, a, L.rot_freq.data, st));
+    AttnParams ap;
+    ap.heads = H; ap.scale = a.scale;
+    AttnIO io;
+    if (prefill) {   // keys and values of the batch, expanded from the cached latents
+        CK(launch_latent_gather(cache, ll.slot_floats, b, a, ll.act2, ct, ll.krb, st));
+        CAT(CAT_DENSE);
+        if (a.dim > 0) CK(launch_dense(ct, ll.act2, R, L.uk.data, R, ll.big3, (int64_t) H * a.dim, T, H * a.dim, R, nullptr, nullptr, 0, 1.f, st));
+        CK(launch_dense(ct, ll.act2, R, L.uv.data, R, ll.big4, VD, T, VD, R, nullptr, nullptr, 0, 1.f, st));
+        CAT(CAT_ATTN);
+        ap.kv_heads = H; ap.dim = DQ; ap.vdim = a.vdim; ap.shared_dim = a.rot_dim;
+        io.q = ll.big2; io.ldq = (int64_t) H * DQ;
+        io.k = ll.big3; io.ldk = (int64_t) H * a.dim;
+        io.ks = ll.krb; io.ldks = a.rot_dim;
+        io.v = ll.big4; io.ldv = VD;
+        io.gate = gate; io.ldg = C; io.gate_mode = 2;
+        CK(launch_attn_prefill_io(io, b, ap, ll.act, ct, st));
+    } else {         // one token per entry against the slot's rows: one key / value head, the key is the whole row, the value its latent part
+        CK(launch_latent_absorb_q(ll.big2, L.uk.data, ct, a, ll.big3, T, st));
+        ap.kv_heads = 1; ap.dim = RW; ap.vdim = R; ap.cache_rows = a.cache_rows;
+        io.q = ll.big3; io.ldq = (int64_t) H * RW;
+        io.k_row = io.v_row = RW;
+        CK(launch_attn_decode_io(io, b, ap, cache, cache, ll.slot_floats, ll.big4, T_F32, st));
+        CK(launch_latent_up_v(ll.big4, L.uv.data, ct, a, gate, C, ll.act, ct, T, st));
+    }
+    CAT(CAT_DENSE);
+    return launch_dense(ct, ll.act, VD, L.out.data, VD, out, W, T, W, VD, nullptr, resid, W, 1.f, st);
+}
+
+// ---- clamped gated feed-forward: x[t] += down(glu(gateup(ll.act[t]))); ll.act stays as it is ----
+static int ff_clamped(pb200_model * m, int T, const DenseW & gateup, const DenseW & down, int ff, float limit, float * x) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int W = ll.width, ct = ll.ctype;
+    CAT(CAT_DENSE);
+    CK(launch_dense(ct, ll.act, W, gateup.data, W, ll.big, 2 * ff, T, 2 * ff, W, nullptr, nullptr, 0, 1.f, st));
+    CAT(CAT_ELEM);
+    CK(launch_clamped_glu(ll.big, ll.act2, ct, T, ff, limit, st));
+    CAT(CAT_DENSE);
+    return launch_dense(ct, ll.act2, ff, down.data, ff, x, W, T, W, ff, nullptr, x, W, 1.f, st);
+}
+static int ff_moe(pb200_model * m, int T, bool prefill, LLayer & L, float * x) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int W = ll.width, ct = ll.ctype;
+    const MoeParams & p = L.moe;
+    const size_t es = esize(ct);
+    CAT(CAT_ELEM);
+    CK(launch_moe_route(ll.act, ct, L.router.data, L.router_b.data, p, W, ll.moe_idx, ll.moe_wt, T, st));
+    if (L.shared_ff > 0) CK(ff_clamped(m, T, L.s_gateup, L.s_down, L.shared_ff, L.shared_limit, x));
+    CAT(CAT_DENSE);
+    if (!prefill || (int64_t) T * p.top <= 64) {
+        CK(launch_moe_gateup_rows(ll.act, ct, L.e_gateup.data, ll.moe_idx, p, W, ll.moe_y, T, st));
+        return launch_moe_down_rows(ll.moe_y, ct, L.e_down.data, ll.moe_idx, ll.moe_wt, p, W, x, T, st);
+    }
+    const int P = T * p.top, E = p.experts;
+    CK(launch_moe_sort(ll.moe_idx, p, T, ll.moe_count, ll.moe_start, ll.moe_perm, st));
+    CK(cudaMemcpyAsync(ll.moe_count_host, ll.moe_count, (size_t) E * 4, cudaMemcpyDeviceToHost, st));
+    CK(cudaMemcpyAsync(ll.moe_count_host + 4096, ll.moe_start, (size_t) E * 4, cudaMemcpyDeviceToHost, st));
+    CK(launch_moe_gather(ll.act, ct, ll.moe_perm, p.top, W, ll.moe_hs, P, st));
+    CK(cudaStreamSynchronize(st));   // the per-expert row counts size the products below
+    const int32_t * cnt = ll.moe_count_host, * start = ll.moe_count_host + 4096;
+    for (int e = 0; e < E; e++)
+        if (cnt[e] > 0)
+            CK(launch_dense(ct, (const uint8_t *) ll.moe_hs + (size_t) start[e] * W * es, W, (const uint8_t *) L.e_gateup.data + (size_t) e * 2 * p.ff * W * es, W,
+                            ll.moe_gu + (int64_t) start[e] * 2 * p.ff, 2 * p.ff, cnt[e], 2 * p.ff, W, nullptr, nullptr, 0, 1.f, st));
+    CK(launch_clamped_glu(ll.moe_gu, ll.moe_y, ct, P, p.ff, p.limit, st));
+    for (int e = 0; e < E; e++)
+        if (cnt[e] > 0)
+            CK(launch_dense(ct, (const uint8_t *) ll.moe_y + (size_t) start[e] * p.ff * es, p.ff, (const uint8_t *) L.e_down.data + (size_t) e * W * p.ff * es, p.ff,
+                            ll.moe_ds + (int64_t) start[e] * W, W, cnt[e], W, p.ff, nullptr, nullptr, 0, 1.f, st));
+    return launch_moe_combine(ll.moe_ds, ll.moe_perm, ll.moe_row_of, ll.moe_wt, p.top, W, x, T, st);
+}
+
+// FRAME_PRENORM: x <- x + mixer(shift(norm1 x)), x <- x + ff(norm2 x), then the weighted sum over the embedding output and the results
+// of all layers so far goes on.  ll.hist plane j holds X_j; ll.x the stream that enters the next layer.
+static int ll_forward_prenorm(pb200_model * m, const BatchView & b, bool prefill, const int32_t * tokens_dev, const int32_t * want_dev, int nW, int lrow0) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int T = b.n_tokens, W = ll.width, ct = ll.ctype, G = ll.norm_groups;
+    const int64_t plane = (int64_t) ll.capT * W;
+    CAT(CAT_ELEM);
+    CK(launch_embed(ll.embed.data, ct, W, tokens_dev, T, ll.x, ll.hist, st));
+    for (size_t ir = 0; ir < ll.runs.size(); ir++) {
+        const LRun & r = ll.runs[ir];
+        LLayer & L = ll.layers[(size_t) r.layer];
+        float * xn = ll.hist + (int64_t) (ir + 1) * plane;
+        CAT(CAT_NORM);
+        CK(launch_group_rmsnorm_shift(ll.x, b, L.norm1.data, G, ll.eps, L.shift.data, ll.state + r.shift_off, ll.slot_floats, ll.act, ct, W, st));
+        if (L.kind == MIX_DECAY) CK(mix_decay(m, b, r, L, ll.x, xn));
+        else if (L.kind == MIX_LATENT) CK(mix_latent(m, b, prefill, r, L, ll.x, xn));
+        else if (L.kind == MIX_ATTENTION) CK(mix_attention(m, b, prefill, r, L, ll.x, xn));
+        else CK(mix_mamba2(m, b, r, L, ll.x, xn));
+        if (L.ff > 0) {
+            CAT(CAT_NORM);
+            CK(launch_group_rmsnorm(xn, nullptr, L.norm2.data, G, ll.eps, ll.act, ct, T, W, st));
+            if (L.ff_kind == FF_MOE) CK(ff_moe(m, T, prefill, L, xn));
+            else CK(ff_clamped(m, T, L.gateup, L.down, L.ff, L.ff_limit, xn));
+        }
+        CAT(CAT_ELEM);
+        CK(launch_depth_average(ll.hist, plane, L.dwa.data, (int) ir + 2, ll.x, (int64_t) T * W, st));
+        if (ll.tap_on) CK(cudaMemcpyAsync(ll.tap + (int64_t) ir * T * W, ll.x, (size_t) T * W * 4, cudaMemcpyDeviceToDevice, st));
+    }
+    if (nW > 0) {
+        CAT(CAT_HEAD);
+        CK(launch_group_rmsnorm(ll.x, want_dev, ll.final_norm.data, G, ll.eps, ll.actw, ct, nW, W, st));
+        CK(launch_dense(ct, ll.actw, W, ll.head.data, W, ll.logits + (int64_t) lrow0 * ll.vocab, ll.vocab, nW, ll.vocab, W, nullptr, nullptr, 0, ll.logit_scale, st));
+    }
+    CAT(-1);
+    return 0;
+}
+
 static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const int32_t * tokens_dev, const int32_t * want_dev, int nW, int lrow0) {
     LayerList & ll = *m->ll;
     cudaStream_t st = m->stream;
     ll.prof_cat.clear();
+    CK(tap_prepare(m, b.n_tokens));
+    if (ll.frame == FRAME_PRENORM) return ll_forward_prenorm(m, b, prefill, tokens_dev, want_dev, nW, lrow0);
     CAT(CAT_ELEM);
     const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
     CK(launch_embed(ll.embed.data, ct, W, tokens_dev, T, ll.x, ll.x0, st));
     float * x = ll.x, * xalt = ll.xalt;
     bool act_ready = false;
-    if (ll.tap_on) {
-        const int64_t need = (int64_t) ll.runs.size() * T * W;
-        if (need > ll.tap_cap) {
-            CK(cudaStreamSynchronize(st));
-            if (ll.tap) cudaFree(ll.tap);
-            ll.tap = nullptr; ll.tap_cap = 0;
-            CK(cudaMalloc((void **) &ll.tap, (size_t) need * 4));
-            ll.tap_cap = need;
-        }
-        ll.tap_floats = need;
-        ll.tap_T = T;
-    }
     for (size_t ir = 0; ir < ll.runs.size(); ir++) {
         const LRun & r = ll.runs[ir];
         LLayer & L = ll.layers[(size_t) r.layer];
@@ -621,7 +1122,6 @@ static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const 
             CK(launch_dense(ct, ll.act2, W, (const uint8_t *) ll.loop_in.data + (size_t) W * esize(ct), 2 * W, xalt, W, T, W, W, nullptr, xalt, W, 1.f, st));
             std::swap(x, xalt);
         }
-        float * sbase = ll.state + r.state_off;
         if (!act_ready) {   // otherwise the previous run's closing norm has already left layernorm(x) * norm1 in ll.act
             CAT(CAT_NORM);
             CK(launch_layernorm(x, nullptr, L.norm1.data, ll.eps, ll.act, ct, T, W, st));
@@ -629,34 +1129,10 @@ static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const 
         act_ready = false;
         // the norm that closes this run also opens the next one, unless a pass of the repeated block (its input mix) or the end comes first
         const LLayer * nextL = (ir + 1 < ll.runs.size() && ll.runs[ir + 1].pass < 0) ? &ll.layers[(size_t) ll.runs[ir + 1].layer] : nullptr;
-        if (L.kind == MIX_ATTENTION) {
-            const AttnParams & a = L.att;
-            const int C = attn_qkvg_cols(a);
-            CAT(CAT_DENSE);
-            CK(launch_dense(ct, ll.act, W, L.qkvg.data, W, ll.big, C, T, C, W, nullptr, nullptr, 0, 1.f, st));
-            float * kc = sbase, * vc = sbase + (int64_t) a.cache_rows * a.kv_heads * a.dim;
-            CAT(CAT_ATTN);
-            CK(launch_attn_kv_store(ll.big, b, a, kc, vc, ll.slot_floats, st));
-            if (prefill) CK(launch_attn_window_prefill(ll.big, b, a, ll.act, ct, st));
-            else CK(launch_attn_window_decode(ll.big, b, a, kc, vc, ll.slot_floats, ll.act, ct, st));
-            CAT(CAT_DENSE);
-            CK(launch_dense(ct, ll.act, (int64_t) a.heads * a.vdim, L.out.data, (int64_t) a.heads * a.vdim, ll.msub, W, T, W, a.heads * a.vdim, nullptr, nullptr, 0,
-                            1.f, st));
-        } else {
-            const Mamba2Params & p = L.ssm;
-            const int U = mamba2_in_cols(p), inner = mamba2_inner(p);
-            CAT(CAT_DENSE);
-            CK(launch_dense(ct, ll.act, W, L.in.data, W, ll.big, U, T, U, W, nullptr, nullptr, 0, 1.f, st));
-            float * cs = sbase, * ss = sbase + (int64_t) (p.conv - 1) * mamba2_conv_channels(p);
-            CAT(CAT_CONV);
-            CK(launch_mamba2_conv(ll.big, b, p, L.conv_w.data, L.conv_b.data, cs, ll.slot_floats, ll.xbc, st));
-            CAT(CAT_SCAN);
-            CK(launch_mamba2_scan(ll.big, ll.xbc, b, p, L.dt_bias.data, L.A_log.data, L.D.data, ss, ll.slot_floats, ll.yssm, st));
-            CAT(CAT_NORM);
-            CK(launch_mamba2_gate_norm(ll.yssm, ll.big, p, L.gnorm.data, ll.eps, ll.act, ct, T, st));
-            CAT(CAT_DENSE);
-            CK(launch_dense(ct, ll.act, inner, L.out.data, inner, ll.msub, W, T, W, inner, nullptr, nullptr, 0, 1.f, st));
-        }
+        if (L.kind == MIX_ATTENTION) CK(mix_attention(m, b, prefill, r, L, nullptr, ll.msub));
+        else if (L.kind == MIX_MAMBA2) CK(mix_mamba2(m, b, r, L, nullptr, ll.msub));
+        else if (L.kind == MIX_DECAY) CK(mix_decay(m, b, r, L, nullptr, ll.msub));
+        else CK(mix_latent(m, b, prefill, r, L, nullptr, ll.msub));
         CAT(CAT_NORM);
         if (L.ff > 0) CK(launch_layernorm_residual_next(ll.msub, L.norm1b.data, L.norm2.data, ll.eps, x, ll.act, ct, T, W, st));
         else if (nextL) { CK(launch_layernorm_residual_next(ll.msub, L.norm1b.data, nextL->norm1.data, ll.eps, x, ll.act, ct, T, W, st)); act_ready = true; }

@@ -1,7 +1,9 @@
 // prima.cpp_b200/csrc/layers.h — launchers of the dense (f32 / bf16 weight) products and of the sequence mixers that the layer-list
 // engine (layers.cu) is built from: windowed attention with kept first tokens, soft-capped scores and a per-head output gate; the
 // Mamba-2 state-space mixer (short causal convolution, selective scan, gated grouped RMS norm); weight-only layer norm with the
-// residual add; tanh-GELU gating.  Every constant of a mechanism is a parameter, nothing is tied to one model.
+// residual add; tanh-GELU gating; RMS norm in groups, token shift and the depth average of layer results; linear attention with a
+// fixed decay per head; softmax attention over a low-rank latent with a shared rotated key part; the clamped gated feed-forward, dense
+// or as a routed mixture of experts.  Every constant of a mechanism is a parameter, nothing is tied to one model.
 // All launchers enqueue on `stream` and return a cudaError_t as int (0 = success).
 #pragma once
 #include <cuda_bf16.h>
@@ -56,6 +58,19 @@ struct AttnParams {
     int window = 0;           // position i sees j <= i with i - j < window ...   (<= 0: every earlier position)
     int keep_first = 0;       // ... or j < keep_first
     int cache_rows = 0;       // rows per slot: positions < keep_first at their own row, later ones in a ring over the rest
+    int shared_dim = 0;       // prompt kernels: the last shared_dim of a key's dim entries come from one array all heads share
+};
+// Where the attention kernels read their inputs (fp32 rows, strides in floats).  Prompt kernels read keys and values of the batch:
+// k rows hold [kv_heads][dim - shared_dim], ks rows [shared_dim]; v rows [kv_heads][vdim].  Decode kernels read q and gate here and
+// the keys / values from the cache, whose rows are k_row / v_row floats apart (kv head h at + h * dim / + h * vdim).
+struct AttnIO {
+    const float * q = nullptr;    int64_t ldq = 0;     // [heads][dim]
+    const float * k = nullptr;    int64_t ldk = 0;
+    const float * ks = nullptr;   int64_t ldks = 0;
+    const float * v = nullptr;    int64_t ldv = 0;
+    const float * gate = nullptr; int64_t ldg = 0;     // gate logits; the output is multiplied by their sigmoid
+    int gate_mode = 0;                                  // 0: no gate, 1: one logit per head, 2: one per output element [heads][vdim]
+    int64_t k_row = 0, v_row = 0;
 };
 __host__ __device__ inline int attn_qkvg_cols(const AttnParams & a) { return a.heads * a.dim + a.kv_heads * a.dim + a.kv_heads * a.vdim + a.heads; }
 // rows of a slot's cache so that every position a later token may still see is present, capped at n_ctx
@@ -73,6 +88,11 @@ int launch_attn_window_prefill(const float * qkvg, const BatchView & b, const At
 // one-token entries: keys and values come from the cache (the token's own row already stored)
 int launch_attn_window_decode(const float * qkvg, const BatchView & b, const AttnParams & a, const float * kcache, const float * vcache,
                               int64_t slot_stride, void * out, int otype, cudaStream_t stream);
+
+// the same two kernels with every input given by an AttnIO
+int launch_attn_prefill_io(const AttnIO & io, const BatchView & b, const AttnParams & a, void * out, int otype, cudaStream_t stream);
+int launch_attn_decode_io(const AttnIO & io, const BatchView & b, const AttnParams & a, const float * kcache, const float * vcache, int64_t slot_stride,
+                          void * out, int otype, cudaStream_t stream);
 
 // ---- Mamba-2 ----
 struct Mamba2Params {
@@ -93,5 +113,81 @@ int launch_mamba2_scan(const float * u, const float * xbc, const BatchView & b, 
 // out[t] = rms_norm_by_group(y[t] * silu(z[t])) * w      (z = first inner columns of u)
 int launch_mamba2_gate_norm(const float * y, const float * u, const Mamba2Params & p, const float * w, float eps, void * out, int otype, int n_tokens,
                             cudaStream_t stream);
+
+// ---- RMS norm in groups, token shift, depth average ----
+// y[r] = x[row] / sqrt(mean over the group (x^2) + eps) * w: the row is cut into `groups` equal consecutive parts, each with its own mean
+int launch_group_rmsnorm(const float * x, const int32_t * rows, const float * w, int groups, float eps, void * y, int otype, int n_rows, int width,
+                         cudaStream_t stream);
+// h = group_rmsnorm(x);  y[t] = h[t] + (h[t-1] - h[t]) * mu, where the token before an entry's first one is the slot's shift state
+// [width] (zeros for a new sequence); afterwards the state holds the h of the entry's last token.  mu == nullptr: y = h, no state.
+int launch_group_rmsnorm_shift(const float * x, const BatchView & b, const float * w, int groups, float eps, const float * mu, float * shift_state,
+                               int64_t slot_stride, void * y, int otype, int width, cudaStream_t stream);
+// out[i] = sum_{j < n} coef[j] * planes[j * plane_stride + i],  i < count
+int launch_depth_average(const float * planes, int64_t plane_stride, const float * coef, int n, float * out, int64_t count, cudaStream_t stream);
+
+// ---- linear attention with a fixed decay per head ----
+struct DecayAttnParams {
+    int heads = 0, dim = 0, vdim = 0;
+    int act = 0;              // 1: q, k, v <- silu(.) before the recurrence
+    float k_scale = 1.f;      // factor on k
+};
+// qkv rows (stride ld floats) hold q [heads][dim] at q_off, k at k_off, v [heads][vdim] at v_off.  Per (entry, head), state S [dim][vdim]
+// f32 carried in the slot:  S <- decay[h] S + k_t v_t^T,  y_t = S^T q_t.   y: [T][heads * vdim]
+int launch_decay_attn(const float * qkv, int64_t ld, int q_off, int k_off, int v_off, const BatchView & b, const DecayAttnParams & p, const float * decay,
+                      float * state, int64_t slot_stride, float * y, cudaStream_t stream);
+// out[t] = y[t] / rms over each of `groups` consecutive parts (* w if w) * act(gate[t]);  act: 0 sigmoid, 1 silu;  gate rows ldg floats apart
+int launch_norm_gate(const float * y, const float * gate, int64_t ldg, int groups, const float * w, int gate_act, float eps, void * out, int otype,
+                     int n_tokens, int inner, cudaStream_t stream);
+
+// ---- attention over a latent ----
+struct LatentParams {
+    int heads = 0, dim = 0, rot_dim = 0, vdim = 0, kv_rank = 0, q_rank = 0;
+    int rot_dims = 0;         // leading entries of the rotated part that turn, in pairs (i, i + rot_dims / 2)
+    float rot_mag = 1.f;      // factor on cos and sin
+    float scale = 1.f;
+    int cache_rows = 0;       // rows of kv_rank + rot_dim floats per slot: [normed latent | rotated shared key part] of every position
+    int own_kv = 1;           // 0: the layer reads another layer's cache and has no down-projection of its own
+};
+__host__ __device__ inline int latent_proj_cols(const LatentParams & p) { return p.q_rank + p.heads * p.vdim + (p.own_kv ? p.kv_rank + p.rot_dim : 0); }
+__host__ __device__ inline int latent_row(const LatentParams & p) { return p.kv_rank + p.rot_dim; }
+// proj: [T][dq | gate | dkv] f32 (one fused projection; dkv only with own_kv).  cq[t] = rmsnorm(dq) * wq -> operand type;
+// with own_kv: cache row of the token's position <- [rmsnorm(dkv[:kv_rank]) * wkv | rotate(dkv[kv_rank:], position)]
+int launch_latent_prep(const float * proj, const BatchView & b, const LatentParams & p, const float * wq, const float * wkv, const float * freq, float eps,
+                       void * cq, int otype, float * cache, int64_t slot_stride, cudaStream_t stream);
+// rotates the last rot_dim entries of every head of q [T][heads][dim + rot_dim] in place by the token's position
+int launch_latent_rope_q(float * q, const BatchView & b, const LatentParams & p, const float * freq, cudaStream_t stream);
+// the batch's own cache rows: latent -> lat [T][kv_rank] (operand type), rotated key part -> kr [T][rot_dim] f32
+int launch_latent_gather(const float * cache, int64_t slot_stride, const BatchView & b, const LatentParams & p, void * lat, int otype, float * kr,
+                         cudaStream_t stream);
+// decode: qa[t][h] = [ W_uk[h]^T q_unrotated[t][h]  (kv_rank) | q_rotated[t][h] (rot_dim) ]:  the score against a cache row is one dot product
+int launch_latent_absorb_q(const float * q, const void * wuk, int wtype, const LatentParams & p, float * qa, int n_tokens, cudaStream_t stream);
+// decode: out[t][h][:] = (W_uv[h] olat[t][h]) * sigmoid(gate[t][h][:])   olat: [T][heads][kv_rank] (the weighted sum of latents)
+int launch_latent_up_v(const float * olat, const void * wuv, int wtype, const LatentParams & p, const float * gate, int64_t ldg, void * out, int otype,
+                       int n_tokens, cudaStream_t stream);
+
+// ---- clamped gated feed-forward, dense or a mixture of experts ----
+// y[t][j] = g s(1.702 g) (u + 1),  g = min(gu[t][j], limit),  u = clamp(gu[t][ff + j], -limit, limit),  s = sigmoid     gu: [T][2 ff] f32
+int launch_clamped_glu(const float * gu, void * y, int otype, int n_tokens, int ff, float limit, cudaStream_t stream);
+struct MoeParams {
+    int experts = 0, top = 0, ff = 0;
+    float limit = 0.f;
+};
+// z = h W_r^T + bias in fp32 (h: the operand-type activations); idx[t][0..top) the experts with the largest z (ties: lower index),
+// wt[t][..] the softmax over the chosen logits
+int launch_moe_route(const void * h, int htype, const float * wr, const float * bias, const MoeParams & p, int width, int32_t * idx, float * wt,
+                     int n_tokens, cudaStream_t stream);
+// few tokens: every (token, chosen expert) streams its expert's rows.  y[t][k][ff] = clamped_glu(expert idx[t][k] of gateup) -> operand type
+int launch_moe_gateup_rows(const void * h, int type, const void * gateup, const int32_t * idx, const MoeParams & p, int width, void * y, int n_tokens,
+                           cudaStream_t stream);
+// x[t] += sum_k wt[t][k] * down[idx[t][k]] y[t][k]      (k in the order of the choice)
+int launch_moe_down_rows(const void * y, int type, const void * down, const int32_t * idx, const float * wt, const MoeParams & p, int width, float * x,
+                         int n_tokens, cudaStream_t stream);
+// many tokens: pairs (t, k) sorted by expert (stable).  count[e], start[e] (exclusive prefix), perm[r] = pair index t * top + k of sorted row r
+int launch_moe_sort(const int32_t * idx, const MoeParams & p, int n_tokens, int32_t * count, int32_t * start, int32_t * perm, cudaStream_t stream);
+// hs[r] = h[perm[r] / top]   (rows of `width` operand-type elements)
+int launch_moe_gather(const void * h, int type, const int32_t * perm, int top, int width, void * hs, int n_rows, cudaStream_t stream);
+// x[t] += sum_k wt[t][k] * ds[row_of[t * top + k]],  row_of = inverse of perm (computed by the kernel from perm)
+int launch_moe_combine(const float * ds, const int32_t * perm, int32_t * row_of, const float * wt, int top, int width, float * x, int n_tokens,
+                       cudaStream_t stream);
 
 }  // namespace pb

@@ -10,41 +10,10 @@
 #include <atomic>
 
 #include "layers.h"
-
-extern std::atomic<uint64_t> g_launches;
+#include "mixers.cuh"
 
 namespace pb {
 namespace {
-
-__device__ __forceinline__ void put(float * p, int64_t i, float v) { p[i] = v; }
-__device__ __forceinline__ void put(__nv_bfloat16 * p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
-__device__ __forceinline__ float wsum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-__device__ __forceinline__ float wmax(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-// sum over the CTA (blockDim.x a multiple of 32, <= 1024); every thread gets the result; `red` is 33 floats of shared memory
-__device__ __forceinline__ float block_sum(float v, float * red) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    v = wsum(v);
-    __syncthreads();   // red may still be read from a previous call
-    if (lane == 0) red[warp] = v;
-    __syncthreads();
-    if (warp == 0) {
-        float s = lane < nw ? red[lane] : 0.f;
-        s = wsum(s);
-        if (lane == 0) red[32] = s;
-    }
-    __syncthreads();
-    return red[32];
-}
-__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
-__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 
 // ---------------------------------------------------------------------------------------------------------------
 template <typename WT>
@@ -154,6 +123,17 @@ __global__ void __launch_bounds__(256) k_argmax_rows(const float * __restrict__ 
 // attention.  Cache row of position p: p itself below keep_first, else keep_first + (p - keep_first) mod ring.
 __device__ __forceinline__ int cache_row(int p, int keep_first, int ring) { return p < keep_first ? p : keep_first + (p - keep_first) % ring; }
 
+// key element d of (token row, kv head): the head's own part, then the part all heads share
+__device__ __forceinline__ float attn_key(const AttnIO & io, int64_t row, int kvh, int d, int DN) {
+    return d < DN ? io.k[row * io.ldk + (int64_t) kvh * DN + d] : io.ks[row * io.ldks + (d - DN)];
+}
+// factor on output element d of head h: sigmoid of a gate logit per head, per element, or none
+__device__ __forceinline__ float attn_gate(const AttnIO & io, int64_t row, int h, int d, int DV) {
+    if (io.gate_mode == 1) return sigmoid_f(io.gate[row * io.ldg + h]);
+    if (io.gate_mode == 2) return sigmoid_f(io.gate[row * io.ldg + (int64_t) h * DV + d]);
+    return 1.f;
+}
+
 __global__ void k_attn_kv_store(const float * __restrict__ qkvg, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
                                 const int32_t * __restrict__ pos0, const int32_t * __restrict__ entry_of, AttnParams a, float * __restrict__ kcache,
                                 float * __restrict__ vcache, int64_t slot_stride) {
@@ -205,7 +185,7 @@ __device__ __forceinline__ void attn_tile_update(float score, bool valid, const 
 }
 
 template <typename OT, int NV>
-__global__ void __launch_bounds__(AQ * 32) k_attn_window_prefill(const float * __restrict__ qkvg, const int32_t * __restrict__ off, AttnParams a,
+__global__ void __launch_bounds__(AQ * 32) k_attn_window_prefill(const AttnIO io, const int32_t * __restrict__ off, AttnParams a,
                                                                   OT * __restrict__ out) {
     extern __shared__ float sm[];
     const int e = blockIdx.z, h = blockIdx.y;
@@ -213,15 +193,14 @@ __global__ void __launch_bounds__(AQ * 32) k_attn_window_prefill(const float * _
     const int q0 = blockIdx.x * AQ;
     if (q0 >= n) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int D = a.dim, DV = a.vdim, C = attn_qkvg_cols(a);
+    const int D = a.dim, DV = a.vdim, DN = a.dim - a.shared_dim;
     const int kvh = h / (a.heads / a.kv_heads);
-    const int koff = a.heads * D + kvh * D, voff = a.heads * D + a.kv_heads * D + kvh * DV, goff = a.heads * D + a.kv_heads * D + a.kv_heads * DV + h;
     float * qs = sm;                       // [AQ][D]
     float * kt = qs + AQ * D;              // [AKT][D + 1]
     float * vt = kt + AKT * (D + 1);       // [AKT][DV]
     const int qi = q0 + warp;              // this warp's query position (entries handled here start at position 0)
     const bool qok = qi < n;
-    for (int d = lane; d < D; d += 32) qs[warp * D + d] = qok ? qkvg[(int64_t) (t_begin + qi) * C + h * D + d] : 0.f;
+    for (int d = lane; d < D; d += 32) qs[warp * D + d] = qok ? io.q[(int64_t) (t_begin + qi) * io.ldq + h * D + d] : 0.f;
     const int q_last = min(q0 + AQ, n) - 1;
     const bool windowed = a.window > 0;
     const int w_lo = windowed ? max(0, q0 - a.window + 1) : 0;          // first key any query of the CTA sees through its window
@@ -237,11 +216,11 @@ __global__ void __launch_bounds__(AQ * 32) k_attn_window_prefill(const float * _
             const int nk = min(AKT, hi - k0);
             for (int i = threadIdx.x; i < AKT * D; i += blockDim.x) {
                 const int j = i / D, d = i - j * D;
-                kt[j * (D + 1) + d] = j < nk ? qkvg[(int64_t) (t_begin + k0 + j) * C + koff + d] : 0.f;
+                kt[j * (D + 1) + d] = j < nk ? attn_key(io, t_begin + k0 + j, kvh, d, DN) : 0.f;
             }
             for (int i = threadIdx.x; i < AKT * DV; i += blockDim.x) {
                 const int j = i / DV, d = i - j * DV;
-                vt[i] = j < nk ? qkvg[(int64_t) (t_begin + k0 + j) * C + voff + d] : 0.f;
+                vt[i] = j < nk ? io.v[(int64_t) (t_begin + k0 + j) * io.ldv + kvh * DV + d] : 0.f;
             }
             __syncthreads();
             if (!qok) continue;
@@ -256,12 +235,11 @@ __global__ void __launch_bounds__(AQ * 32) k_attn_window_prefill(const float * _
         }
     }
     if (!qok) return;
-    const float gate = sigmoid_f(qkvg[(int64_t) (t_begin + qi) * C + goff]);
-    const float inv = l > 0.f ? gate / l : 0.f;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
     for (int c = 0; c < NV; c++) {
         const int d = lane + 32 * c;
-        if (d < DV) put(out, (int64_t) (t_begin + qi) * (a.heads * DV) + h * DV + d, acc[c] * inv);
+        if (d < DV) put(out, (int64_t) (t_begin + qi) * (a.heads * DV) + h * DV + d, acc[c] * inv * attn_gate(io, t_begin + qi, h, d, DV));
     }
 }
 
@@ -272,7 +250,7 @@ __global__ void __launch_bounds__(AQ * 32) k_attn_window_prefill(const float * _
 // shared memory and every thread accumulates queries 4 ty .. +3 x value columns tx + 16 c.  Everything is fp32.
 constexpr int PQ = 64, PK = 64;
 template <typename OT, int NVC>
-__global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const float * __restrict__ qkvg, const int32_t * __restrict__ off, AttnParams a,
+__global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const AttnIO io, const int32_t * __restrict__ off, AttnParams a,
                                                                    OT * __restrict__ out) {
     extern __shared__ float sm[];
     const int e = blockIdx.z, h = blockIdx.y;
@@ -280,9 +258,8 @@ __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const float *
     const int q0 = blockIdx.x * PQ;
     if (q0 >= n) return;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const int D = a.dim, DV = a.vdim, C = attn_qkvg_cols(a);
+    const int D = a.dim, DV = a.vdim, DN = a.dim - a.shared_dim;
     const int kvh = h / (a.heads / a.kv_heads);
-    const int koff = a.heads * D + kvh * D, voff = a.heads * D + a.kv_heads * D + kvh * DV, goff = a.heads * D + a.kv_heads * D + a.kv_heads * DV + h;
     constexpr int PQS = PQ + 4, PKS = PK + 1;   // padded strides: the transposing stores of a tile load spread over the banks
     float * Qt = sm;                    // [D][PQS]  transposed: Qt[d][q]
     float * Kt = Qt + D * PQS;          // [D][PKS]  transposed: Kt[d][k]
@@ -290,7 +267,7 @@ __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const float *
     float * Ps = Vs + PK * DV;          // [PQ][PK + 1]
     for (int i = tid; i < PQ * D; i += 256) {
         const int q = i / D, d = i - q * D;
-        Qt[d * PQS + q] = q0 + q < n ? qkvg[(int64_t) (t_begin + q0 + q) * C + h * D + d] * a.scale : 0.f;
+        Qt[d * PQS + q] = q0 + q < n ? io.q[(int64_t) (t_begin + q0 + q) * io.ldq + h * D + d] * a.scale : 0.f;
     }
     const int q_last = min(q0 + PQ, n) - 1;
     const bool windowed = a.window > 0;
@@ -310,11 +287,11 @@ __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const float *
             __syncthreads();
             for (int i = tid; i < PK * D; i += 256) {
                 const int k = i / D, d = i - k * D;
-                Kt[d * PKS + k] = k < nk ? qkvg[(int64_t) (t_begin + k0 + k) * C + koff + d] : 0.f;
+                Kt[d * PKS + k] = k < nk ? attn_key(io, t_begin + k0 + k, kvh, d, DN) : 0.f;
             }
             for (int i = tid; i < PK * DV; i += 256) {
                 const int k = i / DV, d = i - k * DV;
-                Vs[i] = k < nk ? qkvg[(int64_t) (t_begin + k0 + k) * C + voff + d] : 0.f;
+                Vs[i] = k < nk ? io.v[(int64_t) (t_begin + k0 + k) * io.ldv + kvh * DV + d] : 0.f;
             }
             __syncthreads();
             float s[4][4];
@@ -383,12 +360,11 @@ __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const float *
     for (int i = 0; i < 4; i++) {
         const int qi = q0 + ty * 4 + i;
         if (qi >= n) continue;
-        const float gate = sigmoid_f(qkvg[(int64_t) (t_begin + qi) * C + goff]);
-        const float inv = l[i] > 0.f ? gate / l[i] : 0.f;
+        const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
 #pragma unroll
         for (int c = 0; c < NVC; c++) {
             const int dv = tx + 16 * c;
-            if (dv < DV) put(out, (int64_t) (t_begin + qi) * (a.heads * DV) + h * DV + dv, acc[i][c] * inv);
+            if (dv < DV) put(out, (int64_t) (t_begin + qi) * (a.heads * DV) + h * DV + dv, acc[i][c] * inv * attn_gate(io, t_begin + qi, h, dv, DV));
         }
     }
 }
@@ -398,7 +374,7 @@ __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const float *
 // dimensions.  The 32 partial softmax states are merged in shared memory.
 constexpr int DEC_WARPS = 32, DEC_ROWS = 4;
 template <typename OT, int NV>
-__global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const float * __restrict__ qkvg, const int32_t * __restrict__ slot,
+__global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const AttnIO io, const int32_t * __restrict__ slot,
                                                                        const int32_t * __restrict__ off, const int32_t * __restrict__ pos0, AttnParams a,
                                                                        const float * __restrict__ kcache, const float * __restrict__ vcache,
                                                                        int64_t slot_stride, OT * __restrict__ out) {
@@ -407,21 +383,21 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const flo
     const int t = off[e];
     const int pi = pos0[e];               // position of the query (its own K / V row is in the cache already)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int D = a.dim, DV = a.vdim, C = attn_qkvg_cols(a);
+    const int D = a.dim, DV = a.vdim;
     const int kvh = h / (a.heads / a.kv_heads);
-    const int KD = a.kv_heads * D, VD = a.kv_heads * DV;
+    const int64_t KD = io.k_row, VD = io.v_row;
     const int keep = min(a.keep_first, a.cache_rows), ring = a.cache_rows - keep;
     float * qs = sm;                       // [D], scaled
     float * mm = qs + ((D + 3) & ~3);      // [DEC_WARPS] max, [DEC_WARPS] sum
     float * accs = mm + 2 * DEC_WARPS;     // [DEC_WARPS][NV*32]
-    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = qkvg[(int64_t) t * C + h * D + d] * a.scale;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = io.q[(int64_t) t * io.ldq + h * D + d] * a.scale;
     __syncthreads();
     const float * kc = kcache + (int64_t) slot[e] * slot_stride, * vc = vcache + (int64_t) slot[e] * slot_stride;
     float m = -INFINITY, l = 0.f, acc[NV];
 #pragma unroll
     for (int c = 0; c < NV; c++) acc[c] = 0.f;
     const int rows_used = min(a.cache_rows, pi + 1);
-    const bool vec4 = (D & 3) == 0;
+    const bool vec4 = (D & 3) == 0 && (KD & 3) == 0;
     for (int r0 = warp * DEC_ROWS; r0 < rows_used; r0 += DEC_WARPS * DEC_ROWS) {
         // DEC_ROWS rows per step so that their loads are in flight together; which position does row r hold right now?
         float sc[DEC_ROWS];
@@ -498,12 +474,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const flo
 #pragma unroll
             for (int c = 0; c < NV; c++) o[c] = fmaf(accs[w * NV * 32 + c * 32 + lane], f, o[c]);
         }
-        const float gate = sigmoid_f(qkvg[(int64_t) t * C + a.heads * D + KD + VD + h]);
-        const float inv = L > 0.f ? gate / L : 0.f;
+        const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll
         for (int c = 0; c < NV; c++) {
             const int d = lane + 32 * c;
-            if (d < DV) put(out, (int64_t) t * (a.heads * DV) + h * DV + d, o[c] * inv);
+            if (d < DV) put(out, (int64_t) t * (a.heads * DV) + h * DV + d, o[c] * inv * attn_gate(io, t, h, d, DV));
         }
     }
 }
@@ -687,16 +662,6 @@ __global__ void __launch_bounds__(256) k_mamba2_gate_norm(const float * __restri
         put(out, (int64_t) t * inner + grp * part + i, yr[i] * silu_f(zr[i]) * inv * w[grp * part + i]);
 }
 
-template <typename F> int ck_launch(F && f) {
-    g_launches++;
-    f();
-    return (int) cudaGetLastError();
-}
-template <typename K> int raise_smem(K kernel, size_t bytes) {
-    if (bytes <= 48 * 1024) return 0;
-    return (int) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) bytes);
-}
-
 }  // namespace
 
 int launch_embed(const void * table, int type, int width, const int32_t * tokens, int n_tokens, float * x, float * x_copy, cudaStream_t st) {
@@ -758,67 +723,90 @@ int launch_attn_kv_store(const float * qkvg, const BatchView & b, const AttnPara
         else if ((NVV) <= 2) { constexpr int NV = 2; CALL; }       \
         else if ((NVV) <= 4) { constexpr int NV = 4; CALL; }       \
         else if ((NVV) <= 8) { constexpr int NV = 8; CALL; }       \
+        else if ((NVV) <= 16) { constexpr int NV = 16; CALL; }     \
         else return (int) cudaErrorInvalidValue;                   \
     } while (0)
 
 template <typename OT, int NVC>
-static int attn_prefill_tiled_typed(const float * qkvg, const BatchView & b, const AttnParams & a, OT * out, cudaStream_t st) {
+static int attn_prefill_tiled_typed(const AttnIO & io, const BatchView & b, const AttnParams & a, OT * out, cudaStream_t st) {
     const size_t smem = ((size_t) a.dim * (PQ + 4) + (size_t) a.dim * (PK + 1) + (size_t) PK * a.vdim + (size_t) PQ * (PK + 1)) * sizeof(float);
     int rc = raise_smem(k_attn_window_prefill_tiled<OT, NVC>, smem);
     if (rc) return rc;
     const dim3 grid((unsigned) ((b.max_n + PQ - 1) / PQ), (unsigned) a.heads, (unsigned) b.n_entries);
-    return ck_launch([&] { k_attn_window_prefill_tiled<OT, NVC><<<grid, 256, smem, st>>>(qkvg, b.off, a, out); });
+    return ck_launch([&] { k_attn_window_prefill_tiled<OT, NVC><<<grid, 256, smem, st>>>(io, b.off, a, out); });
 }
 template <typename OT, int NV>
-static int attn_prefill_typed(const float * qkvg, const BatchView & b, const AttnParams & a, OT * out, cudaStream_t st) {
+static int attn_prefill_typed(const AttnIO & io, const BatchView & b, const AttnParams & a, OT * out, cudaStream_t st) {
     const size_t smem = ((size_t) AQ * a.dim + (size_t) AKT * (a.dim + 1) + (size_t) AKT * a.vdim) * sizeof(float);
     int rc = raise_smem(k_attn_window_prefill<OT, NV>, smem);
     if (rc) return rc;
     const dim3 grid((unsigned) ((b.max_n + AQ - 1) / AQ), (unsigned) a.heads, (unsigned) b.n_entries);
-    return ck_launch([&] { k_attn_window_prefill<OT, NV><<<grid, AQ * 32, smem, st>>>(qkvg, b.off, a, out); });
+    return ck_launch([&] { k_attn_window_prefill<OT, NV><<<grid, AQ * 32, smem, st>>>(io, b.off, a, out); });
 }
-int launch_attn_window_prefill(const float * qkvg, const BatchView & b, const AttnParams & a, void * out, int otype, cudaStream_t st) {
+int launch_attn_prefill_io(const AttnIO & io, const BatchView & b, const AttnParams & a, void * out, int otype, cudaStream_t st) {
     if (b.n_tokens <= 0) return 0;
-    if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads != 0 || a.dim <= 0 || a.vdim <= 0) return (int) cudaErrorInvalidValue;
+    if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads != 0 || a.dim <= 0 || a.vdim <= 0 || a.shared_dim < 0 || a.shared_dim > a.dim ||
+        (a.shared_dim > 0 && !io.ks))
+        return (int) cudaErrorInvalidValue;
     static const bool no_tiled = getenv("PB200_ATTN_ROWWISE") != nullptr;   // A/B: the one-warp-per-query kernel for every length
     const size_t tiled_smem = ((size_t) a.dim * (PQ + 4) + (size_t) a.dim * (PK + 1) + (size_t) PK * a.vdim + (size_t) PQ * (PK + 1)) * sizeof(float);
     if (b.max_n > 16 && !no_tiled && tiled_smem <= 220 * 1024) {   // long entries: 64-query tiles; the same numbers up to fp32 summation order
         const int nvc = (a.vdim + 15) / 16;
         if (nvc <= 16) {
             if (otype == T_BF16) {
-                if (nvc <= 2) return attn_prefill_tiled_typed<__nv_bfloat16, 2>(qkvg, b, a, (__nv_bfloat16 *) out, st);
-                if (nvc <= 4) return attn_prefill_tiled_typed<__nv_bfloat16, 4>(qkvg, b, a, (__nv_bfloat16 *) out, st);
-                if (nvc <= 8) return attn_prefill_tiled_typed<__nv_bfloat16, 8>(qkvg, b, a, (__nv_bfloat16 *) out, st);
-                return attn_prefill_tiled_typed<__nv_bfloat16, 16>(qkvg, b, a, (__nv_bfloat16 *) out, st);
+                if (nvc <= 2) return attn_prefill_tiled_typed<__nv_bfloat16, 2>(io, b, a, (__nv_bfloat16 *) out, st);
+                if (nvc <= 4) return attn_prefill_tiled_typed<__nv_bfloat16, 4>(io, b, a, (__nv_bfloat16 *) out, st);
+                if (nvc <= 8) return attn_prefill_tiled_typed<__nv_bfloat16, 8>(io, b, a, (__nv_bfloat16 *) out, st);
+                return attn_prefill_tiled_typed<__nv_bfloat16, 16>(io, b, a, (__nv_bfloat16 *) out, st);
             }
-            if (nvc <= 2) return attn_prefill_tiled_typed<float, 2>(qkvg, b, a, (float *) out, st);
-            if (nvc <= 4) return attn_prefill_tiled_typed<float, 4>(qkvg, b, a, (float *) out, st);
-            if (nvc <= 8) return attn_prefill_tiled_typed<float, 8>(qkvg, b, a, (float *) out, st);
-            return attn_prefill_tiled_typed<float, 16>(qkvg, b, a, (float *) out, st);
+            if (nvc <= 2) return attn_prefill_tiled_typed<float, 2>(io, b, a, (float *) out, st);
+            if (nvc <= 4) return attn_prefill_tiled_typed<float, 4>(io, b, a, (float *) out, st);
+            if (nvc <= 8) return attn_prefill_tiled_typed<float, 8>(io, b, a, (float *) out, st);
+            return attn_prefill_tiled_typed<float, 16>(io, b, a, (float *) out, st);
         }
     }
     const int nv = (a.vdim + 31) / 32;
-    if (otype == T_BF16) PB_NV_DISPATCH(nv, return (attn_prefill_typed<__nv_bfloat16, NV>(qkvg, b, a, (__nv_bfloat16 *) out, st)));
-    else PB_NV_DISPATCH(nv, return (attn_prefill_typed<float, NV>(qkvg, b, a, (float *) out, st)));
+    if (otype == T_BF16) PB_NV_DISPATCH(nv, return (attn_prefill_typed<__nv_bfloat16, NV>(io, b, a, (__nv_bfloat16 *) out, st)));
+    else PB_NV_DISPATCH(nv, return (attn_prefill_typed<float, NV>(io, b, a, (float *) out, st)));
     return 0;
 }
 template <typename OT, int NV>
-static int attn_decode_typed(const float * qkvg, const BatchView & b, const AttnParams & a, const float * kc, const float * vc, int64_t stride, OT * out,
+static int attn_decode_typed(const AttnIO & io, const BatchView & b, const AttnParams & a, const float * kc, const float * vc, int64_t stride, OT * out,
                              cudaStream_t st) {
     const size_t smem = ((size_t) ((a.dim + 3) & ~3) + 2 * DEC_WARPS + (size_t) DEC_WARPS * NV * 32) * sizeof(float);
     int rc = raise_smem(k_attn_window_decode<OT, NV>, smem);
     if (rc) return rc;
     const dim3 grid((unsigned) a.heads, (unsigned) b.n_entries);
-    return ck_launch([&] { k_attn_window_decode<OT, NV><<<grid, DEC_WARPS * 32, smem, st>>>(qkvg, b.slot, b.off, b.pos0, a, kc, vc, stride, out); });
+    return ck_launch([&] { k_attn_window_decode<OT, NV><<<grid, DEC_WARPS * 32, smem, st>>>(io, b.slot, b.off, b.pos0, a, kc, vc, stride, out); });
 }
-int launch_attn_window_decode(const float * qkvg, const BatchView & b, const AttnParams & a, const float * kcache, const float * vcache, int64_t slot_stride,
-                              void * out, int otype, cudaStream_t st) {
+int launch_attn_decode_io(const AttnIO & io, const BatchView & b, const AttnParams & a, const float * kcache, const float * vcache, int64_t slot_stride,
+                          void * out, int otype, cudaStream_t st) {
     if (b.n_tokens <= 0) return 0;
     if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads != 0 || a.dim <= 0 || a.vdim <= 0) return (int) cudaErrorInvalidValue;
     const int nv = (a.vdim + 31) / 32;
-    if (otype == T_BF16) PB_NV_DISPATCH(nv, return (attn_decode_typed<__nv_bfloat16, NV>(qkvg, b, a, kcache, vcache, slot_stride, (__nv_bfloat16 *) out, st)));
-    else PB_NV_DISPATCH(nv, return (attn_decode_typed<float, NV>(qkvg, b, a, kcache, vcache, slot_stride, (float *) out, st)));
+    if (otype == T_BF16) PB_NV_DISPATCH(nv, return (attn_decode_typed<__nv_bfloat16, NV>(io, b, a, kcache, vcache, slot_stride, (__nv_bfloat16 *) out, st)));
+    else PB_NV_DISPATCH(nv, return (attn_decode_typed<float, NV>(io, b, a, kcache, vcache, slot_stride, (float *) out, st)));
     return 0;
+}
+
+// the fused q | k | v | gate projection of the windowed-attention mixer as the kernels' inputs
+static AttnIO attn_io_fused(const float * qkvg, const AttnParams & a) {
+    AttnIO io;
+    const int64_t C = attn_qkvg_cols(a);
+    io.q = qkvg; io.ldq = C;
+    io.k = qkvg + (int64_t) a.heads * a.dim; io.ldk = C;
+    io.v = io.k + (int64_t) a.kv_heads * a.dim; io.ldv = C;
+    io.gate = io.v + (int64_t) a.kv_heads * a.vdim; io.ldg = C; io.gate_mode = 1;
+    io.k_row = (int64_t) a.kv_heads * a.dim; io.v_row = (int64_t) a.kv_heads * a.vdim;
+    return io;
+}
+int launch_attn_window_prefill(const float * qkvg, const BatchView & b, const AttnParams & a, void * out, int otype, cudaStream_t st) {
+    if (a.shared_dim != 0) return (int) cudaErrorInvalidValue;
+    return launch_attn_prefill_io(attn_io_fused(qkvg, a), b, a, out, otype, st);
+}
+int launch_attn_window_decode(const float * qkvg, const BatchView & b, const AttnParams & a, const float * kcache, const float * vcache, int64_t slot_stride,
+                              void * out, int otype, cudaStream_t st) {
+    return launch_attn_decode_io(attn_io_fused(qkvg, a), b, a, kcache, vcache, slot_stride, out, otype, st);
 }
 
 int launch_mamba2_conv(const float * u, const BatchView & b, const Mamba2Params & p, const float * w, const float * bias, float * conv_state,

@@ -1,0 +1,265 @@
+// prima.cpp_b200/csrc/moe.cu — routed mixture of clamped gated experts (declarations and semantics: layers.h).  The router runs in fp32:
+// logits, the choice of the `top` largest (ties: the lower index) and the softmax over the chosen logits.  Two ways through the experts:
+//   few tokens   every (token, chosen expert) pair streams the rows of its expert (weights are read once per pair, mostly from L2 when
+//                tokens share experts); no host round trip, so a decode step stays one replayable graph
+//   many tokens  pairs are sorted by expert (stable counting sort on the device), activations gathered into expert-contiguous rows, the
+//                engine's dense product runs once per expert over its rows, and the results are summed per token in the order of the choice
+// Either way the sum over a token's experts runs in the order of the choice, so a token's result does not depend on the batch around it.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include "layers.h"
+#include "mixers.cuh"
+
+namespace pb {
+namespace {
+
+template <typename WT> struct Pack;
+template <> struct Pack<float> { static constexpr int n = 4; };
+template <> struct Pack<__nv_bfloat16> { static constexpr int n = 8; };
+__device__ __forceinline__ void unpack16(const uint4 & r, float (&f)[4], float) {
+    f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
+}
+__device__ __forceinline__ void unpack16(const uint4 & r, float (&f)[8], __nv_bfloat16) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+// lane's share of sum_k w[k] a[k]; VEC: 16-byte loads (K a multiple of the pack, both rows 16-byte aligned)
+template <typename WT, bool VEC>
+__device__ __forceinline__ float dot_part(const WT * __restrict__ w, const WT * __restrict__ a, int K, int lane) {
+    float acc = 0.f;
+    if constexpr (VEC) {
+        constexpr int V = Pack<WT>::n;
+        for (int k = lane * V; k < K; k += 32 * V) {
+            float wf[V], af[V];
+            unpack16(__ldg(reinterpret_cast<const uint4 *>(w + k)), wf, WT());
+            unpack16(*reinterpret_cast<const uint4 *>(a + k), af, WT());
+#pragma unroll
+            for (int i = 0; i < V; i++) acc = fmaf(wf[i], af[i], acc);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(ld_f(w, k), ld_f(a, k), acc);
+    }
+    return acc;
+}
+
+// one CTA per token: the activations in shared memory as fp32, warps split the experts, warp 0 picks
+template <typename HT>
+__global__ void __launch_bounds__(256) k_moe_route(const HT * __restrict__ h, const float * __restrict__ wr, const float * __restrict__ bias, MoeParams p,
+                                                   int width, int32_t * __restrict__ idx, float * __restrict__ wt) {
+    extern __shared__ float sm[];
+    float * hs = sm;            // [width]
+    float * z = hs + width;     // [experts]
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) hs[i] = ld_f(h, (int64_t) t * width + i);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = warp; e < p.experts; e += (int) (blockDim.x >> 5)) {
+        const float * w = wr + (int64_t) e * width;
+        float acc = 0.f;
+        for (int i = lane; i < width; i += 32) acc = fmaf(w[i], hs[i], acc);
+        acc = wsum(acc);
+        if (lane == 0) z[e] = acc + bias[e];
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float zmax = 0.f, sum = 0.f, mine = 0.f;   // lane k keeps the k-th chosen logit (top <= 32)
+    for (int k = 0; k < p.top; k++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < p.experts; e += 32) {
+            const float v = z[e];
+            if (v > best) { best = v; bi = e; }   // ascending e: the lower index wins a tie inside a lane
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (bi == 0x7fffffff) bi = 0;             // only with non-finite logits
+        if (k == 0) zmax = best;
+        if (lane == k) mine = best;
+        if (lane == 0) { idx[(int64_t) t * p.top + k] = bi; z[bi] = -INFINITY; }
+        __syncwarp();
+    }
+    const float pe = lane < p.top ? expf(mine - zmax) : 0.f;
+    sum = wsum(pe);
+    if (lane < p.top) wt[(int64_t) t * p.top + lane] = pe / sum;
+}
+
+// grid (ceil(ff / 8), pairs): warp -> row j of gate and of up of the pair's expert
+template <typename WT, bool VEC>
+__global__ void __launch_bounds__(256) k_moe_gateup_rows(const WT * __restrict__ h, const WT * __restrict__ gateup, const int32_t * __restrict__ idx, MoeParams p,
+                                                         int width, WT * __restrict__ y) {
+    const int pair = blockIdx.y, t = pair / p.top;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = blockIdx.x * 8 + warp;
+    if (j >= p.ff) return;
+    const WT * we = gateup + (int64_t) idx[pair] * 2 * p.ff * width;
+    const WT * a = h + (int64_t) t * width;
+    float g = dot_part<WT, VEC>(we + (int64_t) j * width, a, width, lane);
+    float u = dot_part<WT, VEC>(we + (int64_t) (p.ff + j) * width, a, width, lane);
+    g = wsum(g);
+    u = wsum(u);
+    if (lane == 0) {
+        g = fminf(g, p.limit);
+        u = fminf(fmaxf(u, -p.limit), p.limit);
+        put(y, (int64_t) pair * p.ff + j, g * sigmoid_f(1.702f * g) * (u + 1.f));
+    }
+}
+// grid (ceil(width / 8), tokens): warp -> output n of the token, summed over its experts in the order of the choice
+template <typename WT, bool VEC>
+__global__ void __launch_bounds__(256) k_moe_down_rows(const WT * __restrict__ y, const WT * __restrict__ down, const int32_t * __restrict__ idx,
+                                                       const float * __restrict__ wt, MoeParams p, int width, float * __restrict__ x) {
+    const int t = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= width) return;
+    float acc = 0.f;
+    for (int k = 0; k < p.top; k++) {
+        const int pair = t * p.top + k;
+        const WT * w = down + ((int64_t) idx[pair] * width + n) * p.ff;
+        const float d = wsum(dot_part<WT, VEC>(w, y + (int64_t) pair * p.ff, p.ff, lane));
+        acc = fmaf(wt[pair], d, acc);
+    }
+    if (lane == 0) x[(int64_t) t * width + n] += acc;
+}
+
+// ---- sort by expert ----
+__global__ void __launch_bounds__(256) k_moe_count(const int32_t * __restrict__ idx, int n_pairs, int32_t * __restrict__ count) {
+    __shared__ float red[33];
+    const int e = blockIdx.x;
+    int c = 0;
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) c += idx[i] == e;
+    const float s = block_sum((float) c, red);   // exact below 2^24 pairs
+    if (threadIdx.x == 0) count[e] = (int32_t) s;
+}
+// one CTA per expert: walks the pairs in order, 256 at a time, and places its own at start[e] + rank (stable)
+__global__ void __launch_bounds__(256) k_moe_place(const int32_t * __restrict__ idx, int n_pairs, const int32_t * __restrict__ count, int32_t * __restrict__ start,
+                                                   int32_t * __restrict__ perm) {
+    __shared__ int wbase[9];
+    const int e = blockIdx.x;
+    int s0 = 0;
+    for (int k = 0; k < e; k++) s0 += count[k];
+    if (threadIdx.x == 0) start[e] = s0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int placed = 0;
+    for (int i0 = 0; i0 < n_pairs; i0 += 256) {
+        const int i = i0 + threadIdx.x;
+        const bool hit = i < n_pairs && idx[i] == e;
+        const unsigned m = __ballot_sync(0xffffffffu, hit);
+        __syncthreads();
+        if (lane == 0) wbase[warp] = __popc(m);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int a = 0;
+            for (int w = 0; w < 8; w++) { const int c = wbase[w]; wbase[w] = a; a += c; }
+            wbase[8] = a;
+        }
+        __syncthreads();
+        if (hit) perm[s0 + placed + wbase[warp] + __popc(m & ((1u << lane) - 1u))] = i;
+        placed += wbase[8];
+    }
+}
+template <typename WT>
+__global__ void k_moe_gather(const WT * __restrict__ h, const int32_t * __restrict__ perm, int top, int width, WT * __restrict__ hs) {
+    const int r = blockIdx.x;
+    const WT * src = h + (int64_t) (perm[r] / top) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) hs[(int64_t) r * width + i] = src[i];
+}
+__global__ void k_moe_invert(const int32_t * __restrict__ perm, int32_t * __restrict__ row_of, int n_pairs) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < n_pairs) row_of[perm[r]] = r;
+}
+__global__ void k_moe_combine(const float * __restrict__ ds, const int32_t * __restrict__ row_of, const float * __restrict__ wt, int top, int width,
+                              float * __restrict__ x) {
+    const int t = blockIdx.x;
+    for (int n = threadIdx.x; n < width; n += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; k++) acc = fmaf(wt[(int64_t) t * top + k], ds[(int64_t) row_of[(int64_t) t * top + k] * width + n], acc);
+        x[(int64_t) t * width + n] += acc;
+    }
+}
+
+template <typename WT> bool vec_ok(const void * a, const void * b, int K) {
+    return K % Pack<WT>::n == 0 && ((uintptr_t) a & 15) == 0 && ((uintptr_t) b & 15) == 0;
+}
+
+}  // namespace
+
+static bool moe_ok(const MoeParams & p) { return p.experts > 0 && p.top > 0 && p.top <= p.experts && p.top <= 32 && p.ff > 0; }
+
+int launch_moe_route(const void * h, int htype, const float * wr, const float * bias, const MoeParams & p, int width, int32_t * idx, float * wt, int n_tokens,
+                     cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (!moe_ok(p)) return (int) cudaErrorInvalidValue;
+    const size_t smem = ((size_t) width + p.experts) * sizeof(float);
+    if (htype == T_BF16) {
+        int rc = raise_smem(k_moe_route<__nv_bfloat16>, smem);
+        if (rc) return rc;
+        return ck_launch([&] { k_moe_route<__nv_bfloat16><<<n_tokens, 256, smem, st>>>((const __nv_bfloat16 *) h, wr, bias, p, width, idx, wt); });
+    }
+    int rc = raise_smem(k_moe_route<float>, smem);
+    if (rc) return rc;
+    return ck_launch([&] { k_moe_route<float><<<n_tokens, 256, smem, st>>>((const float *) h, wr, bias, p, width, idx, wt); });
+}
+int launch_moe_gateup_rows(const void * h, int type, const void * gateup, const int32_t * idx, const MoeParams & p, int width, void * y, int n_tokens,
+                           cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (!moe_ok(p)) return (int) cudaErrorInvalidValue;
+    const dim3 grid((unsigned) ((p.ff + 7) / 8), (unsigned) (n_tokens * p.top));
+    return ck_launch([&] {
+        if (type == T_BF16) {
+            using B = __nv_bfloat16;
+            if (vec_ok<B>(h, gateup, width)) k_moe_gateup_rows<B, true><<<grid, 256, 0, st>>>((const B *) h, (const B *) gateup, idx, p, width, (B *) y);
+            else k_moe_gateup_rows<B, false><<<grid, 256, 0, st>>>((const B *) h, (const B *) gateup, idx, p, width, (B *) y);
+        } else {
+            if (vec_ok<float>(h, gateup, width)) k_moe_gateup_rows<float, true><<<grid, 256, 0, st>>>((const float *) h, (const float *) gateup, idx, p, width, (float *) y);
+            else k_moe_gateup_rows<float, false><<<grid, 256, 0, st>>>((const float *) h, (const float *) gateup, idx, p, width, (float *) y);
+        }
+    });
+}
+int launch_moe_down_rows(const void * y, int type, const void * down, const int32_t * idx, const float * wt, const MoeParams & p, int width, float * x,
+                         int n_tokens, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (!moe_ok(p)) return (int) cudaErrorInvalidValue;
+    const dim3 grid((unsigned) ((width + 7) / 8), (unsigned) n_tokens);
+    return ck_launch([&] {
+        if (type == T_BF16) {
+            using B = __nv_bfloat16;
+            if (vec_ok<B>(y, down, p.ff)) k_moe_down_rows<B, true><<<grid, 256, 0, st>>>((const B *) y, (const B *) down, idx, wt, p, width, x);
+            else k_moe_down_rows<B, false><<<grid, 256, 0, st>>>((const B *) y, (const B *) down, idx, wt, p, width, x);
+        } else {
+            if (vec_ok<float>(y, down, p.ff)) k_moe_down_rows<float, true><<<grid, 256, 0, st>>>((const float *) y, (const float *) down, idx, wt, p, width, x);
+            else k_moe_down_rows<float, false><<<grid, 256, 0, st>>>((const float *) y, (const float *) down, idx, wt, p, width, x);
+        }
+    });
+}
+int launch_moe_sort(const int32_t * idx, const MoeParams & p, int n_tokens, int32_t * count, int32_t * start, int32_t * perm, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (!moe_ok(p) || (int64_t) n_tokens * p.top >= (1 << 24)) return (int) cudaErrorInvalidValue;
+    const int n_pairs = n_tokens * p.top;
+    int rc = ck_launch([&] { k_moe_count<<<p.experts, 256, 0, st>>>(idx, n_pairs, count); });
+    if (rc) return rc;
+    return ck_launch([&] { k_moe_place<<<p.experts, 256, 0, st>>>(idx, n_pairs, count, start, perm); });
+}
+int launch_moe_gather(const void * h, int type, const int32_t * perm, int top, int width, void * hs, int n_rows, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    return ck_launch([&] {
+        if (type == T_BF16) k_moe_gather<__nv_bfloat16><<<n_rows, 128, 0, st>>>((const __nv_bfloat16 *) h, perm, top, width, (__nv_bfloat16 *) hs);
+        else k_moe_gather<float><<<n_rows, 128, 0, st>>>((const float *) h, perm, top, width, (float *) hs);
+    });
+}
+int launch_moe_combine(const float * ds, const int32_t * perm, int32_t * row_of, const float * wt, int top, int width, float * x, int n_tokens,
+                       cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    const int n_pairs = n_tokens * top;
+    int rc = ck_launch([&] { k_moe_invert<<<(unsigned) ((n_pairs + 255) / 256), 256, 0, st>>>(perm, row_of, n_pairs); });
+    if (rc) return rc;
+    return ck_launch([&] { k_moe_combine<<<n_tokens, 256, 0, st>>>(ds, row_of, wt, top, width, x); });
+}
+
+}  // namespace pb

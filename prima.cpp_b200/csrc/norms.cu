@@ -1,0 +1,165 @@
+// prima.cpp_b200/csrc/norms.cu — the frame of a pre-norm layer with token shift and depth average, and the gated steps around its
+// mixers and feed-forward (declarations and semantics: layers.h): RMS norm in groups, the blend of a token's normed input with the
+// previous token's (state per sequence slot), the weighted sum over the results of all layers so far, RMS norm + gate of a linear
+// attention's output, the clamped gated unit.  Everything is fp32; only a value written for a dense product takes its operand type.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include <algorithm>
+
+#include "layers.h"
+#include "mixers.cuh"
+
+namespace pb {
+namespace {
+
+constexpr int MAX_NORM_GROUPS = 64;
+
+// 1 / sqrt(mean(part^2) + eps) of every group of a row -> inv[0..groups) in shared memory; all threads of the CTA take part
+__device__ __forceinline__ void group_inv_rms(const float * __restrict__ row, int width, int groups, float eps, float * inv, float * red) {
+    const int part = width / groups;
+    for (int g = 0; g < groups; g++) {
+        float q = 0.f;
+        for (int i = threadIdx.x; i < part; i += blockDim.x) { const float v = row[g * part + i]; q = fmaf(v, v, q); }
+        const float s = block_sum(q, red);
+        if (threadIdx.x == 0) inv[g] = 1.f / sqrtf(s / (float) part + eps);
+    }
+    __syncthreads();
+}
+
+template <typename OT>
+__global__ void __launch_bounds__(256) k_group_rmsnorm(const float * __restrict__ x, const int32_t * __restrict__ rows, const float * __restrict__ w, int groups,
+                                                       float eps, OT * __restrict__ y, int width) {
+    __shared__ float red[33];
+    __shared__ float inv[MAX_NORM_GROUPS];
+    const int r = blockIdx.x;
+    const float * in = x + (int64_t) (rows ? rows[r] : r) * width;
+    group_inv_rms(in, width, groups, eps, inv, red);
+    const int part = width / groups;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) put(y, (int64_t) r * width + i, in[i] * inv[i / part] * w[i]);
+}
+
+// one CTA per token: the norm of the token and of the one before it (recomputed: a second read of a row that is in L2), then the blend
+template <typename OT>
+__global__ void __launch_bounds__(256) k_group_rmsnorm_shift(const float * __restrict__ x, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
+                                                             const int32_t * __restrict__ entry_of, const float * __restrict__ w, int groups, float eps,
+                                                             const float * __restrict__ mu, const float * __restrict__ shift_state, int64_t slot_stride,
+                                                             OT * __restrict__ y, int width) {
+    __shared__ float red[33];
+    __shared__ float inv[MAX_NORM_GROUPS], invp[MAX_NORM_GROUPS];
+    const int t = blockIdx.x;
+    const int e = entry_of[t];
+    const bool first = t == off[e];
+    const float * in = x + (int64_t) t * width;
+    group_inv_rms(in, width, groups, eps, inv, red);
+    if (!first) group_inv_rms(in - width, width, groups, eps, invp, red);
+    const float * st = shift_state + (int64_t) slot[e] * slot_stride;
+    const int part = width / groups;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float h = in[i] * inv[i / part] * w[i];
+        const float hp = first ? st[i] : in[i - width] * invp[i / part] * w[i];
+        put(y, (int64_t) t * width + i, h + (hp - h) * mu[i]);
+    }
+}
+// one CTA per entry: the normed input of its last token becomes the slot's shift state
+__global__ void __launch_bounds__(256) k_shift_state(const float * __restrict__ x, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
+                                                     const float * __restrict__ w, int groups, float eps, float * __restrict__ shift_state, int64_t slot_stride,
+                                                     int width) {
+    __shared__ float red[33];
+    __shared__ float inv[MAX_NORM_GROUPS];
+    const int e = blockIdx.x;
+    const float * in = x + (int64_t) (off[e + 1] - 1) * width;
+    group_inv_rms(in, width, groups, eps, inv, red);
+    float * st = shift_state + (int64_t) slot[e] * slot_stride;
+    const int part = width / groups;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) st[i] = in[i] * inv[i / part] * w[i];
+}
+
+__global__ void k_depth_average(const float * __restrict__ planes, int64_t plane_stride, const float * __restrict__ coef, int n, float * __restrict__ out,
+                                int64_t count) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float acc = 0.f;
+    for (int j = 0; j < n; j++) acc = fmaf(coef[j], planes[(int64_t) j * plane_stride + i], acc);
+    out[i] = acc;
+}
+
+template <typename OT>
+__global__ void __launch_bounds__(256) k_norm_gate(const float * __restrict__ y, const float * __restrict__ gate, int64_t ldg, int part,
+                                                   const float * __restrict__ w, int gate_act, float eps, OT * __restrict__ out, int inner) {
+    __shared__ float red[33];
+    const int t = blockIdx.x, grp = blockIdx.y;
+    const float * yr = y + (int64_t) t * inner + grp * part;
+    const float * gr = gate + (int64_t) t * ldg + grp * part;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) q = fmaf(yr[i], yr[i], q);
+    const float inv = 1.f / sqrtf(block_sum(q, red) / (float) part + eps);
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+        float v = yr[i] * inv;
+        if (w) v *= w[grp * part + i];
+        v *= gate_act == 0 ? sigmoid_f(gr[i]) : silu_f(gr[i]);
+        put(out, (int64_t) t * inner + grp * part + i, v);
+    }
+}
+
+template <typename OT>
+__global__ void k_clamped_glu(const float * __restrict__ gu, OT * __restrict__ y, int n_tokens, int ff, float limit) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t) n_tokens * ff) return;
+    const int64_t t = i / ff, j = i - t * ff;
+    const float g = fminf(gu[t * 2 * ff + j], limit);
+    const float u = fminf(fmaxf(gu[t * 2 * ff + ff + j], -limit), limit);
+    put(y, i, g * sigmoid_f(1.702f * g) * (u + 1.f));
+}
+
+}  // namespace
+
+int launch_group_rmsnorm(const float * x, const int32_t * rows, const float * w, int groups, float eps, void * y, int otype, int n_rows, int width,
+                         cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    if (groups <= 0 || groups > MAX_NORM_GROUPS || width % groups != 0) return (int) cudaErrorInvalidValue;
+    return ck_launch([&] {
+        if (otype == T_BF16) k_group_rmsnorm<__nv_bfloat16><<<n_rows, 256, 0, st>>>(x, rows, w, groups, eps, (__nv_bfloat16 *) y, width);
+        else k_group_rmsnorm<float><<<n_rows, 256, 0, st>>>(x, rows, w, groups, eps, (float *) y, width);
+    });
+}
+int launch_group_rmsnorm_shift(const float * x, const BatchView & b, const float * w, int groups, float eps, const float * mu, float * shift_state,
+                               int64_t slot_stride, void * y, int otype, int width, cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    if (!mu) return launch_group_rmsnorm(x, nullptr, w, groups, eps, y, otype, b.n_tokens, width, st);
+    if (groups <= 0 || groups > MAX_NORM_GROUPS || width % groups != 0 || !shift_state) return (int) cudaErrorInvalidValue;
+    int rc = ck_launch([&] {
+        if (otype == T_BF16)
+            k_group_rmsnorm_shift<__nv_bfloat16><<<b.n_tokens, 256, 0, st>>>(x, b.slot, b.off, b.entry_of, w, groups, eps, mu, shift_state, slot_stride,
+                                                                             (__nv_bfloat16 *) y, width);
+        else k_group_rmsnorm_shift<float><<<b.n_tokens, 256, 0, st>>>(x, b.slot, b.off, b.entry_of, w, groups, eps, mu, shift_state, slot_stride, (float *) y, width);
+    });
+    if (rc) return rc;
+    return ck_launch([&] { k_shift_state<<<b.n_entries, 256, 0, st>>>(x, b.slot, b.off, w, groups, eps, shift_state, slot_stride, width); });
+}
+int launch_depth_average(const float * planes, int64_t plane_stride, const float * coef, int n, float * out, int64_t count, cudaStream_t st) {
+    if (count <= 0 || n <= 0) return 0;
+    return ck_launch([&] { k_depth_average<<<(unsigned) ((count + 255) / 256), 256, 0, st>>>(planes, plane_stride, coef, n, out, count); });
+}
+int launch_norm_gate(const float * y, const float * gate, int64_t ldg, int groups, const float * w, int gate_act, float eps, void * out, int otype,
+                     int n_tokens, int inner, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (groups <= 0 || inner % groups != 0) return (int) cudaErrorInvalidValue;
+    const dim3 grid((unsigned) n_tokens, (unsigned) groups);
+    return ck_launch([&] {
+        if (otype == T_BF16) k_norm_gate<__nv_bfloat16><<<grid, 256, 0, st>>>(y, gate, ldg, inner / groups, w, gate_act, eps, (__nv_bfloat16 *) out, inner);
+        else k_norm_gate<float><<<grid, 256, 0, st>>>(y, gate, ldg, inner / groups, w, gate_act, eps, (float *) out, inner);
+    });
+}
+int launch_clamped_glu(const float * gu, void * y, int otype, int n_tokens, int ff, float limit, cudaStream_t st) {
+    const int64_t n = (int64_t) n_tokens * ff;
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned) ((n + 255) / 256);
+    return ck_launch([&] {
+        if (otype == T_BF16) k_clamped_glu<__nv_bfloat16><<<grid, 256, 0, st>>>(gu, (__nv_bfloat16 *) y, n_tokens, ff, limit);
+        else k_clamped_glu<float><<<grid, 256, 0, st>>>(gu, (float *) y, n_tokens, ff, limit);
+    });
+}
+
+}  // namespace pb
