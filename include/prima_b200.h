@@ -288,9 +288,9 @@ PB200_API int pb200_batch_step(pb200_model * m, int n_entries, const pb200_batch
 /* white-box tests: on != 0 keeps the residual stream after every layer run of the next batches; read it with
  * pb200_debug_read(m, "layers", host, runs * tokens * n_embd) */
 PB200_API int pb200_debug_tap_layers(pb200_model * m, int on);
-/* measurement: on != 0 records CUDA events around every launch of the next batches; pb200_debug_read(m, "profile", host, 8) returns the
+/* measurement: on != 0 records CUDA events around every launch of the next batches; pb200_debug_read(m, "profile", host, 10) returns the
  * device milliseconds of the last batch per category: dense products, attention, convolution, scan, norms, element-wise, output head,
- * [7] total.  Events serialise nothing but forbid overlap between launches; leave it off when timing whole steps. */
+ * [7] total, [8] routed experts, [9] the small steps around latent attention.  Events serialise nothing but forbid overlap between launches; leave it off when timing whole steps. */
 PB200_API int pb200_debug_profile(pb200_model * m, int on);
 
 #ifdef __cplusplus

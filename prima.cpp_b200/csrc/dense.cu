@@ -21,6 +21,8 @@ namespace pb {
 int launch_dense_tc(const __nv_bfloat16 * A, int64_t lda, const __nv_bfloat16 * W, int64_t ldw, float * C, int64_t ldc, int T, int N, int K,
                     const float * bias, const float * resid, int64_t ldr, float alpha, cudaStream_t stream);   // dense_tc.cu
 bool dense_tc_ok(int T, int N, int K, int64_t lda, int64_t ldw, const void * A, const void * W);
+int launch_dense_tc_grouped(const __nv_bfloat16 * A, int64_t lda, const __nv_bfloat16 * W, int64_t ldw, int64_t w_stride, float * C, int64_t ldc,
+                            const int32_t * start, const int32_t * count, int groups, int max_rows, int N, int K, cudaStream_t st);
 
 namespace {
 
@@ -192,6 +194,15 @@ int dense_typed(const WT * A, int64_t lda, const WT * W, int64_t ldw, float * C,
 
 int dense_uses_tensor_cores(int type, int T, int N, int K, int64_t lda, int64_t ldw) {
     return type == T_BF16 && T > rows_max_t() && dense_tc_ok(T, N, K, lda, ldw, nullptr, nullptr) ? 1 : 0;
+}
+
+int dense_grouped_ok(int type, int N, int K, int64_t lda, int64_t ldw, int64_t w_stride, const void * A, const void * W) {
+    return type == T_BF16 && w_stride % 8 == 0 && dense_tc_ok(1, N, K, lda, ldw, A, W) ? 1 : 0;
+}
+int launch_dense_grouped(int type, const void * A, int64_t lda, const void * W, int64_t ldw, int64_t w_stride, float * C, int64_t ldc, const int32_t * start,
+                         const int32_t * count, int groups, int max_rows, int N, int K, cudaStream_t st) {
+    if (!dense_grouped_ok(type, N, K, lda, ldw, w_stride, A, W)) return (int) cudaErrorInvalidValue;
+    return launch_dense_tc_grouped((const __nv_bfloat16 *) A, lda, (const __nv_bfloat16 *) W, ldw, w_stride, C, ldc, start, count, groups, max_rows, N, K, st);
 }
 
 int launch_dense(int type, const void * A, int64_t lda, const void * W, int64_t ldw, float * C, int64_t ldc, int T, int N, int K, const float * bias,

@@ -34,6 +34,10 @@ struct TcParams {
     float alpha;
     int T, N, K;
     int * abort_flag;
+    // grouped: rows [grp_start[g], + grp_count[g]) of A times the g-th matrix of W (grp_w_stride elements apart) into the same rows of C.
+    // The counts live on the device: blockIdx.y numbers the token tiles of all groups in a row (group 0's tiles, then group 1's, ...), the
+    // grid has room for the most tiles there can be (rows / BN + groups) and a CTA past the last tile leaves at once.
+    const int32_t * grp_start; const int32_t * grp_count; int64_t grp_w_stride; int groups;
 };
 
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {   // K-major, SWIZZLE_128B: rows of 128 B, 8-row groups 1024 B apart
@@ -79,12 +83,27 @@ __device__ __forceinline__ void stage_rows(uint32_t dst, const __nv_bfloat16 * M
 
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) k_dense_tc(const __grid_constant__ TcParams P) {
+    const __nv_bfloat16 * Am = P.A, * Wm = P.W;
+    float * Cm = P.C;
+    int Tn = P.T, tile_y = blockIdx.y;
+    if (P.grp_count) {
+        int g = 0;
+        for (; g < P.groups; g++) {
+            const int nt = (P.grp_count[g] + BN - 1) / BN;
+            if (tile_y < nt) break;
+            tile_y -= nt;
+        }
+        if (g >= P.groups) return;   // the whole CTA, before any barrier or TMEM allocation
+        Tn = P.grp_count[g];
+        const int64_t r0 = P.grp_start[g];
+        Am += r0 * P.lda; Cm += r0 * P.ldc; Wm += (int64_t) g * P.grp_w_stride;
+    }
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int A_BYTES = TC_BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
     TcCtl * ctl = reinterpret_cast<TcCtl *>(smem + TC_STAGES * STAGE);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * TC_BM, t0 = blockIdx.y * BN;
+    const int n0 = blockIdx.x * TC_BM, t0 = tile_y * BN;
     const int nk = (P.K + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -115,8 +134,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_dense_tc(const __grid_constan
             const int s = u % TC_STAGES;
             if (u >= TC_STAGES) mbar_wait(&ctl->empty[s], (uint32_t) ((u / TC_STAGES - 1) & 1), cta_abort, P.abort_flag);
             const uint32_t base = smem_u32(smem + s * STAGE);
-            stage_rows<TC_BM>(base, P.W, P.ldw, n0, P.N, u * TC_BK, P.K, p);
-            stage_rows<BN>(base + A_BYTES, P.A, P.lda, t0, P.T, u * TC_BK, P.K, p);
+            stage_rows<TC_BM>(base, Wm, P.ldw, n0, P.N, u * TC_BK, P.K, p);
+            stage_rows<BN>(base + A_BYTES, Am, P.lda, t0, Tn, u * TC_BK, P.K, p);
             asm volatile("cp.async.commit_group;" ::: "memory");
             if (u - signalled >= TC_LAG) {
                 asm volatile("cp.async.wait_group 2;" ::: "memory");
@@ -153,7 +172,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_dense_tc(const __grid_constan
         const int n = n0 + quad * 32 + lane;
         const float bias = (P.bias && n < P.N) ? P.bias[n] : 0.f;
         for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 16) {
-            if (t0 + c0 >= P.T) break;                                   // uniform over the warp
+            if (t0 + c0 >= Tn) break;                                   // uniform over the warp
             uint32_t v[16];
             const uint32_t taddr = tmem + ((uint32_t) (quad * 32) << 16) + (uint32_t) c0;
             asm volatile(
@@ -167,10 +186,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_dense_tc(const __grid_constan
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
                     const int t = t0 + c0 + i;
-                    if (t < P.T) {
+                    if (t < Tn) {
                         float y = P.alpha * __uint_as_float(v[i]) + bias;
                         if (P.resid) y += P.resid[(int64_t) t * P.ldr + n];
-                        P.C[(int64_t) t * P.ldc + n] = y;
+                        Cm[(int64_t) t * P.ldc + n] = y;
                     }
                 }
             }
@@ -191,7 +210,7 @@ int launch_tc(const TcParams & P, cudaStream_t st) {
     static FuncAttrCache cache;
     cudaError_t e = ensure_dyn_smem(cache, (const void *) k_dense_tc<BN>, tc_smem<BN>(), BN == 256);
     if (e != cudaSuccess) return (int) e;
-    const dim3 grid((unsigned) ((P.N + TC_BM - 1) / TC_BM), (unsigned) ((P.T + BN - 1) / BN));
+    const dim3 grid((unsigned) ((P.N + TC_BM - 1) / TC_BM), (unsigned) ((P.T + BN - 1) / BN + (P.grp_count ? P.groups : 0)));
     g_launches++;
     k_dense_tc<BN><<<grid, TC_THREADS, tc_smem<BN>(), st>>>(P);
     return (int) cudaGetLastError();
@@ -206,8 +225,17 @@ bool dense_tc_ok(int T, int N, int K, int64_t lda, int64_t ldw, const void * A, 
 
 int launch_dense_tc(const __nv_bfloat16 * A, int64_t lda, const __nv_bfloat16 * W, int64_t ldw, float * C, int64_t ldc, int T, int N, int K, const float * bias,
                     const float * resid, int64_t ldr, float alpha, cudaStream_t st) {
-    TcParams P{A, lda, W, ldw, C, ldc, bias, resid, ldr, alpha, T, N, K, abort_flag()};
+    TcParams P{A, lda, W, ldw, C, ldc, bias, resid, ldr, alpha, T, N, K, abort_flag(), nullptr, nullptr, 0, 0};
     return T <= 64 ? launch_tc<64>(P, st) : T <= 128 ? launch_tc<128>(P, st) : launch_tc<256>(P, st);
+}
+
+int launch_dense_tc_grouped(const __nv_bfloat16 * A, int64_t lda, const __nv_bfloat16 * W, int64_t ldw, int64_t w_stride, float * C, int64_t ldc,
+                            const int32_t * start, const int32_t * count, int groups, int max_rows, int N, int K, cudaStream_t st) {
+    if (groups <= 0 || max_rows <= 0) return 0;
+    // T bounds the grid only (all groups together hold max_rows rows); the kernel reads each group's own count
+    TcParams P{A, lda, W, ldw, C, ldc, nullptr, nullptr, 0, 1.f, max_rows, N, K, abort_flag(), start, count, w_stride, groups};
+    const int avg = (max_rows + groups - 1) / groups;   // the token tile follows the expected rows of a group
+    return avg <= 64 ? launch_tc<64>(P, st) : avg <= 128 ? launch_tc<128>(P, st) : launch_tc<256>(P, st);
 }
 
 }  // namespace pb

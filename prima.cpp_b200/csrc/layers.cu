@@ -138,6 +138,8 @@ struct LayerList {
     void *act = nullptr, *act2 = nullptr, *actw = nullptr;
     // FRAME_PRENORM and its mixers: results of all layers [layers + 1][capT][width]; further fp32 and operand-type scratch
     float *hist = nullptr, *big2 = nullptr, *big3 = nullptr, *big4 = nullptr, *krb = nullptr;
+    float * lat_part = nullptr;     // partial results of the split latent decode attention, [entries][splits][heads][kv_rank + 2]
+    size_t lat_part_cap = 0;
     // mixture of experts: pairs (token, choice)
     int32_t *moe_idx = nullptr, *moe_perm = nullptr, *moe_row_of = nullptr, *moe_count = nullptr, *moe_start = nullptr, *moe_count_host = nullptr;
     float *moe_wt = nullptr, *moe_gu = nullptr, *moe_ds = nullptr;
@@ -156,7 +158,7 @@ struct LayerList {
     bool prof_on = false;
     std::vector<cudaEvent_t> prof_ev;
     std::vector<int> prof_cat;
-    float prof_ms[8] = {0};
+    float prof_ms[10] = {0};
     // decode steps replayed as CUDA graphs, one per (entries, wanted rows); the batch's metadata lives at fixed device addresses
     struct StepGraph { cudaGraphExec_t exec = nullptr; int seen = 0; uint64_t launches = 0; };
     std::map<uint64_t, StepGraph> graphs;
@@ -744,6 +746,7 @@ void ll_free(pb200_model * m) {
     if (ll->greedy_host) cudaFreeHost(ll->greedy_host);
     if (ll->logits_host) cudaFreeHost(ll->logits_host);
     if (ll->moe_count_host) cudaFreeHost(ll->moe_count_host);
+    if (ll->lat_part) cudaFree(ll->lat_part);
     if (ll->tap) cudaFree(ll->tap);
     for (cudaEvent_t e : ll->prof_ev) cudaEventDestroy(e);
     delete ll;
@@ -867,6 +870,18 @@ static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
         CK(cudaMallocHost((void **) &ll.greedy_host, (size_t) cW * 4));
         ll.capT = cT; ll.capW = cW;
     }
+    size_t need_part = 0;
+    for (const LLayer & L : ll.layers)
+        if (L.kind == MIX_LATENT)
+            need_part = std::max(need_part, (size_t) nE * (size_t) latent_decode_splits(ll.n_ctx) * (size_t) L.lat.heads * (size_t) (L.lat.kv_rank + 2));
+    if (need_part > ll.lat_part_cap) {
+        CK(cudaStreamSynchronize(m->stream));
+        ll_drop_graphs(ll);
+        if (ll.lat_part) cudaFree(ll.lat_part);
+        ll.lat_part = nullptr; ll.lat_part_cap = 0;
+        CK(cudaMalloc((void **) &ll.lat_part, need_part * 2 * 4));
+        ll.lat_part_cap = need_part * 2;
+    }
     const size_t need_meta = (size_t) 2 * T + 3 * (size_t) nE + 1 + (size_t) nW + 64;
     if (need_meta > ll.meta_cap) {
         CK(cudaStreamSynchronize(m->stream));
@@ -892,7 +907,7 @@ static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
 // One homogeneous ragged batch through every layer run.  `prefill`: every entry starts at position 0 (keys and values are read from
 // the batch); otherwise every entry brings one token (keys and values come from the slot's cache).  Rows `want_dev[0..nW)` (token
 // indices of the batch) go through the final norm and the output head into logits rows lrow0 ...
-enum : int { CAT_DENSE = 0, CAT_ATTN = 1, CAT_CONV = 2, CAT_SCAN = 3, CAT_NORM = 4, CAT_ELEM = 5, CAT_HEAD = 6, N_CAT = 7 };
+enum : int { CAT_DENSE = 0, CAT_ATTN = 1, CAT_CONV = 2, CAT_SCAN = 3, CAT_NORM = 4, CAT_ELEM = 5, CAT_HEAD = 6, CAT_TOTAL = 7, CAT_MOE = 8, CAT_LATENT = 9 };
 static int prof_mark(pb200_model * m, int cat) {   // an event before the launch of a category; the next mark (or the end) closes its interval
     LayerList & ll = *m->ll;
     if (!ll.prof_on) return 0;
@@ -981,11 +996,11 @@ static int mix_latent(pb200_model * m, const BatchView & b, bool prefill, const 
     const float * gate = ll.big + a.q_rank;
     CAT(CAT_DENSE);
     CK(launch_dense(ct, ll.act, W, L.lproj.data, W, ll.big, C, T, C, W, nullptr, nullptr, 0, 1.f, st));
-    CAT(CAT_ATTN);
+    CAT(CAT_LATENT);
     CK(launch_latent_prep(ll.big, b, a, L.dq_norm.data, L.dkv_norm.data, L.rot_freq.data, ll.eps, ll.act2, ct, cache, ll.slot_floats, st));
     CAT(CAT_DENSE);
     CK(launch_dense(ct, ll.act2, a.q_rank, L.uq.data, a.q_rank, ll.big2, (int64_t) H * DQ, T, H * DQ, a.q_rank, nullptr, nullptr, 0, 1.f, st));
-    CAT(CAT_ATTN);
+    CAT(CAT_LATENT);
     CK(launch_latent_rope_q(ll.big2, b, a, L.rot_freq.data, st));
     AttnParams ap;
     ap.heads = H; ap.scale = a.scale;
@@ -1003,12 +1018,18 @@ static int mix_latent(pb200_model * m, const BatchView & b, bool prefill, const 
         io.v = ll.big4; io.ldv = VD;
         io.gate = gate; io.ldg = C; io.gate_mode = 2;
         CK(launch_attn_prefill_io(io, b, ap, ll.act, ct, st));
-    } else {         // one token per entry against the slot's rows: one key / value head, the key is the whole row, the value its latent part
+    } else if (T == b.n_entries && R <= 512) {   // one token per entry: the key up-projection folded into the query, rows split over CTAs
         CK(launch_latent_absorb_q(ll.big2, L.uk.data, ct, a, ll.big3, T, st));
+        CAT(CAT_ATTN);
+        CK(launch_latent_decode(ll.big3, b, a, cache, ll.slot_floats, latent_decode_splits(a.cache_rows), ll.lat_part, L.uv.data, ct, gate, C, ll.act, ct, st));
+    } else {         // the same through the shared decode kernel: one key / value head, the key is the whole row, the value its latent part
+        CK(launch_latent_absorb_q(ll.big2, L.uk.data, ct, a, ll.big3, T, st));
+        CAT(CAT_ATTN);
         ap.kv_heads = 1; ap.dim = RW; ap.vdim = R; ap.cache_rows = a.cache_rows;
         io.q = ll.big3; io.ldq = (int64_t) H * RW;
         io.k_row = io.v_row = RW;
         CK(launch_attn_decode_io(io, b, ap, cache, cache, ll.slot_floats, ll.big4, T_F32, st));
+        CAT(CAT_LATENT);
         CK(launch_latent_up_v(ll.big4, L.uv.data, ct, a, gate, C, ll.act, ct, T, st));
     }
     CAT(CAT_DENSE);
@@ -1033,19 +1054,27 @@ static int ff_moe(pb200_model * m, int T, bool prefill, LLayer & L, float * x) {
     const int W = ll.width, ct = ll.ctype;
     const MoeParams & p = L.moe;
     const size_t es = esize(ct);
-    CAT(CAT_ELEM);
+    CAT(CAT_MOE);
     CK(launch_moe_route(ll.act, ct, L.router.data, L.router_b.data, p, W, ll.moe_idx, ll.moe_wt, T, st));
     if (L.shared_ff > 0) CK(ff_clamped(m, T, L.s_gateup, L.s_down, L.shared_ff, L.shared_limit, x));
-    CAT(CAT_DENSE);
+    CAT(CAT_MOE);
     if (!prefill || (int64_t) T * p.top <= 64) {
         CK(launch_moe_gateup_rows(ll.act, ct, L.e_gateup.data, ll.moe_idx, p, W, ll.moe_y, T, st));
         return launch_moe_down_rows(ll.moe_y, ct, L.e_down.data, ll.moe_idx, ll.moe_wt, p, W, x, T, st);
     }
     const int P = T * p.top, E = p.experts;
     CK(launch_moe_sort(ll.moe_idx, p, T, ll.moe_count, ll.moe_start, ll.moe_perm, st));
+    CK(launch_moe_gather(ll.act, ct, ll.moe_perm, p.top, W, ll.moe_hs, P, st));
+    if (dense_grouped_ok(ct, 2 * p.ff, W, W, W, (int64_t) 2 * p.ff * W, ll.moe_hs, L.e_gateup.data) &&
+        dense_grouped_ok(ct, W, p.ff, p.ff, p.ff, (int64_t) W * p.ff, ll.moe_y, L.e_down.data)) {
+        // all experts in one launch each way; the row counts never leave the device
+        CK(launch_dense_grouped(ct, ll.moe_hs, W, L.e_gateup.data, W, (int64_t) 2 * p.ff * W, ll.moe_gu, 2 * p.ff, ll.moe_start, ll.moe_count, E, P, 2 * p.ff, W, st));
+        CK(launch_clamped_glu(ll.moe_gu, ll.moe_y, ct, P, p.ff, p.limit, st));
+        CK(launch_dense_grouped(ct, ll.moe_y, p.ff, L.e_down.data, p.ff, (int64_t) W * p.ff, ll.moe_ds, W, ll.moe_start, ll.moe_count, E, P, W, p.ff, st));
+        return launch_moe_combine(ll.moe_ds, ll.moe_perm, ll.moe_row_of, ll.moe_wt, p.top, W, x, T, st);
+    }
     CK(cudaMemcpyAsync(ll.moe_count_host, ll.moe_count, (size_t) E * 4, cudaMemcpyDeviceToHost, st));
     CK(cudaMemcpyAsync(ll.moe_count_host + 4096, ll.moe_start, (size_t) E * 4, cudaMemcpyDeviceToHost, st));
-    CK(launch_moe_gather(ll.act, ct, ll.moe_perm, p.top, W, ll.moe_hs, P, st));
     CK(cudaStreamSynchronize(st));   // the per-expert row counts size the products below
     const int32_t * cnt = ll.moe_count_host, * start = ll.moe_count_host + 4096;
     for (int e = 0; e < E; e++)
@@ -1161,12 +1190,12 @@ static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const 
 static int prof_collect(pb200_model * m) {   // after the stream has been synchronised
     LayerList & ll = *m->ll;
     if (!ll.prof_on) return 0;
-    for (int c = 0; c < 8; c++) ll.prof_ms[c] = 0.f;
+    for (int c = 0; c < 10; c++) ll.prof_ms[c] = 0.f;
     for (size_t i = 0; i + 1 < ll.prof_cat.size(); i++) {
         float ms = 0.f;
         CK(cudaEventElapsedTime(&ms, ll.prof_ev[i], ll.prof_ev[i + 1]));
         if (ll.prof_cat[i] >= 0) ll.prof_ms[ll.prof_cat[i]] += ms;
-        ll.prof_ms[7] += ms;
+        ll.prof_ms[CAT_TOTAL] += ms;
     }
     return 0;
 }
@@ -1323,8 +1352,8 @@ int ll_debug_read(pb200_model * m, const char * name, float * host, int64_t n) {
     LayerList & ll = *m->ll;
     cudaSetDevice(m->device);
     CK(cudaStreamSynchronize(m->stream));
-    if (strcmp(name, "profile") == 0) {   // ms of the last batch: dense, attention, convolution, scan, norms, element-wise, head, [7] = total
-        if (n > 8) return PB200_EINVAL;
+    if (strcmp(name, "profile") == 0) {   // ms of the last batch: dense, attention, convolution, scan, norms, element-wise, head, [7] = total,
+        if (n > 10) return PB200_EINVAL;   // [8] = routed experts, [9] = the small steps around latent attention (norm + rotation, gather, folds)
         memcpy(host, ll.prof_ms, (size_t) n * 4);
         return 0;
     }

@@ -32,6 +32,12 @@ struct BatchView {
 // The result of a row does not depend on the other rows of the call beyond the choice between the small-batch and the tiled kernel.
 int launch_dense(int type, const void * A, int64_t lda, const void * W, int64_t ldw, float * C, int64_t ldc, int T, int N, int K,
                  const float * bias, const float * resid, int64_t ldr, float alpha, cudaStream_t stream);
+// Grouped product in one launch: rows [start[g], start[g] + count[g]) of A times the g-th matrix of W (w_stride elements apart, [N][K]
+// each) into the same rows of C, g < groups; start / count are device arrays and no group has more than max_rows rows.  Tensor-core
+// kernel only (bf16, aligned shapes): dense_grouped_ok says whether it applies; otherwise the caller multiplies group by group.
+int dense_grouped_ok(int type, int N, int K, int64_t lda, int64_t ldw, int64_t w_stride, const void * A, const void * W);
+int launch_dense_grouped(int type, const void * A, int64_t lda, const void * W, int64_t ldw, int64_t w_stride, float * C, int64_t ldc, const int32_t * start,
+                         const int32_t * count, int groups, int max_rows, int N, int K, cudaStream_t stream);
 // 1: the tensor-core kernel takes this shape (bf16, aligned K / strides); informational (bench, tests)
 int dense_uses_tensor_cores(int type, int T, int N, int K, int64_t lda, int64_t ldw);
 
@@ -164,6 +170,12 @@ int launch_latent_absorb_q(const float * q, const void * wuk, int wtype, const L
 // decode: out[t][h][:] = (W_uv[h] olat[t][h]) * sigmoid(gate[t][h][:])   olat: [T][heads][kv_rank] (the weighted sum of latents)
 int launch_latent_up_v(const float * olat, const void * wuv, int wtype, const LatentParams & p, const float * gate, int64_t ldg, void * out, int otype,
                        int n_tokens, cudaStream_t stream);
+
+// decode attention of one-token entries over the slot's rows, split over `splits` CTAs per (entry, 16 heads), then the merge, the
+// value up-projection and the gate in a second kernel.  part: scratch of n_entries * splits * heads * (kv_rank + 2) floats.
+inline int latent_decode_splits(int cache_rows) { return cache_rows >= 2048 ? 64 : cache_rows >= 64 ? cache_rows / 32 : 1; }
+int launch_latent_decode(const float * qa, const BatchView & b, const LatentParams & p, const float * cache, int64_t slot_stride, int splits, float * part,
+                         const void * wuv, int wtype, const float * gate, int64_t ldg, void * out, int otype, cudaStream_t stream);
 
 // ---- clamped gated feed-forward, dense or a mixture of experts ----
 // y[t][j] = g s(1.702 g) (u + 1),  g = min(gu[t][j], limit),  u = clamp(gu[t][ff + j], -limit, limit),  s = sigmoid     gu: [T][2 ff] f32

@@ -45,6 +45,22 @@ __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-
 __device__ __forceinline__ float ld_f(const float * p, int64_t i) { return p[i]; }
 __device__ __forceinline__ float ld_f(const __nv_bfloat16 * p, int64_t i) { return __bfloat162float(p[i]); }
 
+// a lane's share of sum_i a[i] * b[i], i = lane, lane + 32, ...; a in global memory (eight loads in flight), b in shared memory
+template <typename T>
+__device__ __forceinline__ float dot_lane8(const T * __restrict__ a, const float * b, int n, int lane) {
+    float acc = 0.f;
+    int i = lane;
+    for (; i + 7 * 32 < n; i += 8 * 32) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = ld_f(a, i + 32 * u);
+#pragma unroll
+        for (int u = 0; u < 8; u++) acc = fmaf(v[u], b[i + 32 * u], acc);
+    }
+    for (; i < n; i += 32) acc = fmaf(ld_f(a, i), b[i], acc);
+    return acc;
+}
+
 template <typename F> int ck_launch(F && f) {
     g_launches++;
     f();

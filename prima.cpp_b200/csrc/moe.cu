@@ -3,7 +3,8 @@
 //   few tokens   every (token, chosen expert) pair streams the rows of its expert (weights are read once per pair, mostly from L2 when
 //                tokens share experts); no host round trip, so a decode step stays one replayable graph
 //   many tokens  pairs are sorted by expert (stable counting sort on the device), activations gathered into expert-contiguous rows, the
-//                engine's dense product runs once per expert over its rows, and the results are summed per token in the order of the choice
+//                engine's dense product runs over every expert's rows (one grouped tensor-core launch each way whose row counts stay on
+//                the device; expert by expert where that kernel does not apply), and the results are summed per token in the order of the choice
 // Either way the sum over a token's experts runs in the order of the choice, so a token's result does not depend on the batch around it.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -57,10 +58,7 @@ __global__ void __launch_bounds__(256) k_moe_route(const HT * __restrict__ h, co
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int e = warp; e < p.experts; e += (int) (blockDim.x >> 5)) {
-        const float * w = wr + (int64_t) e * width;
-        float acc = 0.f;
-        for (int i = lane; i < width; i += 32) acc = fmaf(w[i], hs[i], acc);
-        acc = wsum(acc);
+        const float acc = wsum(dot_lane8(wr + (int64_t) e * width, hs, width, lane));
         if (lane == 0) z[e] = acc + bias[e];
     }
     __syncthreads();

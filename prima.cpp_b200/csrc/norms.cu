@@ -16,14 +16,25 @@ namespace {
 
 constexpr int MAX_NORM_GROUPS = 64;
 
-// 1 / sqrt(mean(part^2) + eps) of every group of a row -> inv[0..groups) in shared memory; all threads of the CTA take part
+// 1 / sqrt(mean(part^2) + eps) of every group of a row -> inv[0..groups) in shared memory; all threads of the CTA take part.
+// Several groups: a warp sums a whole group (no CTA-wide reduction, one barrier); one group: the CTA sums it together.
 __device__ __forceinline__ void group_inv_rms(const float * __restrict__ row, int width, int groups, float eps, float * inv, float * red) {
     const int part = width / groups;
-    for (int g = 0; g < groups; g++) {
+    if (groups == 1) {
         float q = 0.f;
-        for (int i = threadIdx.x; i < part; i += blockDim.x) { const float v = row[g * part + i]; q = fmaf(v, v, q); }
+        for (int i = threadIdx.x; i < part; i += blockDim.x) { const float v = row[i]; q = fmaf(v, v, q); }
         const float s = block_sum(q, red);
-        if (threadIdx.x == 0) inv[g] = 1.f / sqrtf(s / (float) part + eps);
+        if (threadIdx.x == 0) inv[0] = 1.f / sqrtf(s / (float) part + eps);
+    } else {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+        for (int g = warp; g < groups; g += nw) {
+            float q0 = 0.f, q1 = 0.f;
+            int i = lane;
+            for (; i + 32 < part; i += 64) { const float a = row[g * part + i], b = row[g * part + i + 32]; q0 = fmaf(a, a, q0); q1 = fmaf(b, b, q1); }
+            if (i < part) { const float a = row[g * part + i]; q0 = fmaf(a, a, q0); }
+            const float s = wsum(q0 + q1);
+            if (lane == 0) inv[g] = 1.f / sqrtf(s / (float) part + eps);
+        }
     }
     __syncthreads();
 }
@@ -44,22 +55,23 @@ __global__ void __launch_bounds__(256) k_group_rmsnorm(const float * __restrict_
 template <typename OT>
 __global__ void __launch_bounds__(256) k_group_rmsnorm_shift(const float * __restrict__ x, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
                                                              const int32_t * __restrict__ entry_of, const float * __restrict__ w, int groups, float eps,
-                                                             const float * __restrict__ mu, const float * __restrict__ shift_state, int64_t slot_stride,
+                                                             const float * __restrict__ mu, float * __restrict__ shift_state, int64_t slot_stride,
                                                              OT * __restrict__ y, int width) {
     __shared__ float red[33];
     __shared__ float inv[MAX_NORM_GROUPS], invp[MAX_NORM_GROUPS];
     const int t = blockIdx.x;
     const int e = entry_of[t];
-    const bool first = t == off[e];
+    const bool first = t == off[e], only = first && off[e + 1] == t + 1;
     const float * in = x + (int64_t) t * width;
     group_inv_rms(in, width, groups, eps, inv, red);
     if (!first) group_inv_rms(in - width, width, groups, eps, invp, red);
-    const float * st = shift_state + (int64_t) slot[e] * slot_stride;
+    float * st = shift_state + (int64_t) slot[e] * slot_stride;
     const int part = width / groups;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float h = in[i] * inv[i / part] * w[i];
         const float hp = first ? st[i] : in[i - width] * invp[i / part] * w[i];
         put(y, (int64_t) t * width + i, h + (hp - h) * mu[i]);
+        if (only) st[i] = h;   // an entry of one token: this CTA is the state's only reader and writer (k_shift_state serves longer entries)
     }
 }
 // one CTA per entry: the normed input of its last token becomes the slot's shift state
@@ -69,6 +81,7 @@ __global__ void __launch_bounds__(256) k_shift_state(const float * __restrict__ 
     __shared__ float red[33];
     __shared__ float inv[MAX_NORM_GROUPS];
     const int e = blockIdx.x;
+    if (off[e + 1] - off[e] <= 1) return;   // written by k_group_rmsnorm_shift
     const float * in = x + (int64_t) (off[e + 1] - 1) * width;
     group_inv_rms(in, width, groups, eps, inv, red);
     float * st = shift_state + (int64_t) slot[e] * slot_stride;
@@ -135,7 +148,7 @@ int launch_group_rmsnorm_shift(const float * x, const BatchView & b, const float
                                                                              (__nv_bfloat16 *) y, width);
         else k_group_rmsnorm_shift<float><<<b.n_tokens, 256, 0, st>>>(x, b.slot, b.off, b.entry_of, w, groups, eps, mu, shift_state, slot_stride, (float *) y, width);
     });
-    if (rc) return rc;
+    if (rc || b.max_n <= 1) return rc;   // one-token entries have written their state themselves
     return ck_launch([&] { k_shift_state<<<b.n_entries, 256, 0, st>>>(x, b.slot, b.off, w, groups, eps, shift_state, slot_stride, width); });
 }
 int launch_depth_average(const float * planes, int64_t plane_stride, const float * coef, int n, float * out, int64_t count, cudaStream_t st) {

@@ -244,8 +244,8 @@ class Model:
         self.lib.check(self.lib.c.pb200_debug_profile(self.h, int(on)), "debug_profile")
 
     def profile_ms(self) -> dict:
-        v = self.debug_read("profile", 8)
-        return dict(zip(("dense", "attention", "conv", "scan", "norm", "elementwise", "head", "total"), (float(x) for x in v)))
+        v = self.debug_read("profile", 10)
+        return dict(zip(("dense", "attention", "conv", "scan", "norm", "elementwise", "head", "total", "experts", "latent_steps"), (float(x) for x in v)))
 
     def tap_layers(self, on: bool = True) -> None:
         self.lib.check(self.lib.c.pb200_debug_tap_layers(self.h, int(on)), "debug_tap_layers")

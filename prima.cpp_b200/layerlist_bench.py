@@ -1,6 +1,6 @@
-"""Throughput of the layer-list family (Vamidra) at sizes that resemble a real model's layers, beside the closest existing model
-(the Llama graph over Q4_K weights) at equal width / feed-forward / head counts / number of layer runs, random weights.
-Used by ``bench.py --arch vamidra``; prints one JSON line.
+"""Throughput of the layer-list family at sizes that resemble a real model's layers, random weights, beside the closest existing model at
+equal width / feed-forward / head sizes / number of layer runs: Vamidra beside the Llama graph over Q4_K weights (``bench.py --arch
+vamidra``), Mumizen beside Vamidra (``bench.py --arch mumizen``, :func:`run_mumizen`).  Prints one JSON line.
 
 Per size: prompt tokens/s (one sequence of 512 and 2048 tokens) and decode tokens/s (batch 1 and 8 at a 1024-token context) of both
 models through their public entry points (host token ids in, host logits / greedy tokens out), the device time of a prompt and of a
@@ -61,6 +61,8 @@ def peaks():
 
 
 def run(args, pkg, lib):
+    if args.arch == "mumizen":
+        return run_mumizen(args, pkg, lib)
     import numpy as np
     import torch
     hbm, tflops, src = peaks()
@@ -241,6 +243,170 @@ def run(args, pkg, lib):
                                             "vamidra_ms_per_run": v["prompt2048_device_ms"]["attention"] / 3}
         del q, kc, vc, o, pos
         out["like_kernels"] = probes
+        res["sizes"][key] = out
+        torch.cuda.empty_cache()
+    res["gpu_launches"] = int(lib.c.pb200_kernel_launches())
+    print(json.dumps(res))
+    return res
+
+
+# ---------------------------------------------------------------------------------------------------------------
+MUMIZEN_SIZES = {
+    "w2048": dict(heads=16, dim=128, vdim=128, rot_dim=64, kv_rank=512, q_rank=1024, experts=16, top=2, expert_ff=2048, shared_ff=2048, groups=4),
+    "w4096": dict(heads=32, dim=128, vdim=128, rot_dim=64, kv_rank=512, q_rank=1536, experts=16, top=2, expert_ff=4096, shared_ff=4096, groups=8),
+}
+
+
+def mumizen_config(s, z):
+    """Six layers at the width / feed-forward of SIZES: decay attention of both kinds and latent attention (one layer reads another's
+    latent cache), four dense feed-forwards and two mixtures of experts with a shared expert."""
+    H = z["heads"]
+    decay = [1.0 - 2.0 ** (-5 - 7 * h / max(H - 1, 1)) for h in range(H)]
+    lin = {"heads": H, "dim": z["dim"], "vdim": z["vdim"], "decay": decay}
+    lat = {"heads": H, "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"], "q_rank": z["q_rank"],
+           "scale": (z["dim"] + z["rot_dim"]) ** -0.5,
+           "rot": {"base": 10000.0, "dims": z["rot_dim"], "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    dense = {"kind": "dense", "ff": s["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared_ff"], "limit": 7.0}}
+    layers = [{"type": "retention", "mixer": lin, "mlp": dense}, {"type": "lightning", "mixer": lin, "mlp": moe},
+              {"type": "latent_attention", "mixer": lat, "mlp": dense}, {"type": "latent_attention", "mixer": dict(lat, kv_from=2), "mlp": moe},
+              {"type": "lightning", "mixer": lin, "mlp": dense}, {"type": "latent_attention", "mixer": lat, "mlp": dense}]
+    return {"architecture": "Mumizen", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-6, "groups": z["groups"]}, "layers": layers}
+
+
+def mumizen_products(cfg, prompt):
+    """((N, K) of the plain dense products, expert weight elements touched) of one token through all layers, the head not included."""
+    W, out, expert = cfg["width"], [], 0
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        if l["type"] in ("lightning", "retention"):
+            out += [(2 * m["heads"] * m["dim"] + 2 * m["heads"] * m["vdim"], W), (W, m["heads"] * m["vdim"])]
+        else:
+            H = m["heads"]
+            out += [(m["q_rank"] + H * m["vdim"] + (0 if "kv_from" in m else m["kv_rank"] + m["rot_dim"]), W), (H * (m["dim"] + m["rot_dim"]), m["q_rank"]),
+                    (W, H * m["vdim"])]
+            if prompt:
+                out += [(H * m["dim"], m["kv_rank"]), (H * m["vdim"], m["kv_rank"])]
+        f = l["mlp"]
+        if f["kind"] == "dense":
+            out += [(2 * f["ff"], W), (W, f["ff"])]
+        else:
+            out += [(2 * f["shared"]["ff"], W), (W, f["shared"]["ff"])]
+            expert += f["router"]["top"] * 3 * f["expert"]["ff"] * W
+    return out, expert
+
+
+def run_mumizen(args, pkg, lib):
+    """Mumizen beside Vamidra at equal width / feed-forward / head size and six layer runs each: whole-model prompt and decode throughput
+    through the public entry points, device time per kernel category, and for every pair of like kernels the distance from its roofline."""
+    import numpy as np
+    import torch
+    hbm, tflops, src = peaks()
+    res = {"metric": "Mumizen prompt / decode throughput beside Vamidra at equal size", "impl": "b200", "arch": "Mumizen", "n_gpus": 1, "dtype": "bf16",
+           "data": "synthetic random weights", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}, "sizes": {}}
+    rng = np.random.default_rng(0)
+    CTX = 1024
+
+    def measure(m, vocab):
+        v = {}
+        for T in (512, 2048):
+            toks = rng.integers(0, vocab, T).tolist()
+
+            def prompt():
+                sl = m.seq_alloc()
+                m.batch_step([(sl, toks, [T - 1])])
+                m.seq_free(sl)
+            for _ in range(3):
+                prompt()
+            reps = max(3, args.steps // 16)
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                prompt()
+            v[f"prompt{T}_tok_s"] = T / ((time.perf_counter() - t0) / reps)
+            m.profile(True)
+            prompt()
+            v[f"prompt{T}_device_ms"] = m.profile_ms()
+            m.profile(False)
+        for B in (1, 8):
+            slots = [m.seq_alloc() for _ in range(B)]
+            ctx = rng.integers(0, vocab, CTX).tolist()
+            m.batch_step([(sl, ctx, []) for sl in slots])
+            step = lambda: m.batch_step([(sl, [5], []) for sl in slots], greedy=True)   # noqa: E731
+            for _ in range(max(3, args.warmup)):
+                step()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                step()
+            dt = (time.perf_counter() - t0) / args.steps
+            v[f"decode_b{B}_tok_s"] = B / dt
+            v[f"decode_b{B}_ms_per_step"] = dt * 1e3
+            m.profile(True)
+            step()
+            v[f"decode_b{B}_device_ms"] = m.profile_ms()
+            m.profile(False)
+            for sl in slots:
+                m.seq_free(sl)
+        return v
+
+    for key in ([args.arch_size] if args.arch_size != "all" else list(SIZES)):
+        s, z = SIZES[key], MUMIZEN_SIZES[key]
+        W, V = s["width"], s["vocab"]
+        out = {"config": dict(z, width=W, ff=s["ff"], vocab=V), "layers": 6}
+        # ---------------- the new design ----------------
+        cfg = mumizen_config(s, z)
+        m = pkg.Model.from_config(cfg, dtype="bfloat16", n_ctx=4096, n_seq=16)
+        m.synth(0, 7)
+        m.finalize()
+        a = measure(m, V)
+        m.close()
+        H, D, Dv, Dr, R = z["heads"], z["dim"], z["vdim"], z["rot_dim"], z["kv_rank"]
+        n_lin = sum(l["type"] != "latent_attention" for l in cfg["layers"])
+        n_lat = 6 - n_lin
+        n_norm = 6 + 6 + sum(1 for l in cfg["layers"])      # norm1 (+ shift) and norm2 per layer; the depth average rides in `elementwise`
+        for T in (512, 2048):
+            pm = a[f"prompt{T}_device_ms"]
+            prods, expert = mumizen_products(cfg, True)
+            fl = 2.0 * sum(n * k for n, k in prods) * T
+            a[f"prompt{T}_dense_frac_of_tensor_peak"] = fl / pm["dense"] / 1e9 / tflops
+            a[f"prompt{T}_experts_frac_of_tensor_peak"] = 2.0 * expert * T / pm["experts"] / 1e9 / tflops
+            a[f"prompt{T}_attention_tflops"] = n_lat * 2.0 * (D + Dr + Dv) * H * T * (T + 1) / 2 / pm["attention"] / 1e9
+            a[f"prompt{T}_scan_state_updates_per_ns"] = n_lin * T * H * D * Dv / pm["scan"] / 1e6
+            a[f"prompt{T}_norm_gbs"] = 12 * T * W * 6.0 / pm["norm"] / 1e6
+        prods, expert = mumizen_products(cfg, False)
+        wb = 2.0 * sum(n * k for n, k in prods)
+        a["weight_bytes_per_token"] = wb + 2.0 * expert + 2.0 * V * W
+        for B in (1, 8):
+            pm = a[f"decode_b{B}_device_ms"]
+            a[f"decode_b{B}_dense_frac_of_hbm_peak"] = wb / pm["dense"] / 1e6 / hbm
+            a[f"decode_b{B}_experts_frac_of_hbm_peak"] = 2.0 * expert * B / pm["experts"] / 1e6 / hbm     # b = 8: the most bytes the 8 tokens can touch
+            a[f"decode_b{B}_attention_gbs"] = n_lat * B * CTX * (R + Dr) * 4.0 / pm["attention"] / 1e6
+            a[f"decode_b{B}_whole_step_frac_of_hbm_peak"] = a["weight_bytes_per_token"] / a[f"decode_b{B}_ms_per_step"] / 1e6 / hbm
+        out["mumizen"] = a
+        # ---------------- the closest existing model: Vamidra, equal sizes, 6 layer runs ----------------
+        vcfg = vamidra_config(s)
+        m = pkg.Model.from_config(vcfg, dtype="bfloat16", n_ctx=4096, n_seq=16)
+        m.synth(0, 7)
+        m.finalize()
+        b = measure(m, V)
+        m.close()
+        shapes = dense_shapes(s, vcfg)
+        for T in (512, 2048):
+            pm = b[f"prompt{T}_device_ms"]
+            b[f"prompt{T}_dense_frac_of_tensor_peak"] = 2.0 * sum(n * k for n, k in shapes) * T / pm["dense"] / 1e9 / tflops
+            vis = sum(min(i + 1, s["window"]) + max(0, min(s["keep_first"], i + 1 - s["window"])) for i in range(T))
+            b[f"prompt{T}_attention_tflops"] = 3 * 4.0 * s["dim"] * s["heads"] * vis / pm["attention"] / 1e9
+            b[f"prompt{T}_scan_state_updates_per_ns"] = 3 * T * s["ssm_heads"] * s["state"] * s["vdim"] / pm["scan"] / 1e6
+            b[f"prompt{T}_norm_gbs"] = (12 * T * W * 6.0 + 3 * T * s["ssm_heads"] * s["vdim"] * 10.0) / pm["norm"] / 1e6
+        wbv = 2.0 * sum(n * k for n, k in shapes)
+        b["weight_bytes_per_token"] = wbv + 2.0 * V * W
+        rows = min(CTX, s["window"] + s["keep_first"])
+        for B in (1, 8):
+            pm = b[f"decode_b{B}_device_ms"]
+            b[f"decode_b{B}_dense_frac_of_hbm_peak"] = wbv / pm["dense"] / 1e6 / hbm
+            b[f"decode_b{B}_attention_gbs"] = 3 * B * rows * s["kv_heads"] * 2 * s["dim"] * 4.0 / pm["attention"] / 1e6
+            b[f"decode_b{B}_whole_step_frac_of_hbm_peak"] = b["weight_bytes_per_token"] / b[f"decode_b{B}_ms_per_step"] / 1e6 / hbm
+        out["vamidra"] = b
         res["sizes"][key] = out
         torch.cuda.empty_cache()
     res["gpu_launches"] = int(lib.c.pb200_kernel_launches())

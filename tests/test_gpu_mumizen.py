@@ -313,7 +313,8 @@ ODD = {
     "odd_sizes": lambda: config([retention_layer(heads=3, dim=10, vdim=13, decay=(0.0, 0.5, 0.9), mlp=dense_ff(50)),
                                  latent_layer(heads=5, dim=6, rot_dim=6, vdim=9, kv_rank=21, q_rank=17, rot={"base": 500.0, "dims": 4}, mlp=moe_ff(7, 3, 18, 1.0, 10, 0.5)),
                                  lightning_layer(heads=2, dim=9, vdim=35, decay=(0.7, 0.95))], width=30, vocab=67, groups=5),
-    "wide_recurrent_heads": lambda: config([lightning_layer(heads=1, dim=136, vdim=72, decay=(0.98,)), retention_layer(heads=2, dim=128, vdim=33, decay=(0.9, 0.99))],
+    "wide_recurrent_heads": lambda: config([lightning_layer(heads=1, dim=136, vdim=72, decay=(0.98,)), retention_layer(heads=2, dim=128, vdim=33, decay=(0.9, 0.99)),
+                                            retention_layer(heads=1, dim=264, vdim=70, decay=(0.95,)), lightning_layer(heads=2, dim=40, vdim=17, decay=(0.9, 0.8))],
                                             width=64, vocab=31, groups=2),
     "wide_latent": lambda: config([latent_layer(heads=2, dim=40, rot_dim=16, vdim=136, kv_rank=260, q_rank=48,
                                                 rot={"base": 10000.0, "dims": 16, "scaling": {"factor": 16.0, "original": 32, "fast": 4.0, "slow": 0.5}})],
