@@ -323,15 +323,16 @@ ODD = {
 }
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", F32_TOL), ("bfloat16", BF16_TOL)])
 @pytest.mark.parametrize("which", sorted(ODD))
-def test_other_sizes(pkg, cuda, which):
+def test_other_sizes(pkg, cuda, which, dtype, tol):
     cfg = ODD[which]()
     bits, W = R.random_weights(cfg, seed=16)
     toks = tokens_for(cfg, 45, 7)
     want, _ = R.forward(cfg, W, toks)
-    m = load(pkg, cfg, bits)
-    check(run_whole(m, toks), want, F32_TOL)
-    check(run_decoded(m, toks, 20), want, F32_TOL)
+    m = load(pkg, cfg, bits, dtype)
+    check(run_whole(m, toks), want, tol)
+    check(run_decoded(m, toks, 20), want, tol)
     m.close()
 
 
