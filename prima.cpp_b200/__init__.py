@@ -2,9 +2,10 @@
 
 The product is ``libprima_b200.so`` (CUDA kernels + C++ decode engine, ``include/prima_b200.h``) and
 ``libggml-b200.so`` (the same kernels behind the reference's ggml-backend vtables, ``include/ggml_b200.h``).
-The same library and model object serve a second family of models, the layer list (first design: Vamidra): dense bf16 / f32
-weights from a safetensors directory, windowed attention with kept first tokens and Mamba-2 mixers, sequence slots and a
-ragged batch step (``Model.from_dir`` / ``Model.batch_step``), driven by :class:`BatchScheduler`.
+The same library and model object serve a second family of models, the layer list: dense bf16 / f32 weights from a safetensors
+directory, sequence slots and a ragged batch step (``Model.from_dir`` / ``Model.batch_step``), driven by :class:`BatchScheduler`.
+Designs: Vamidra (windowed attention with kept first tokens, Mamba-2 mixers) and Mumizen (decay linear attention, attention over a
+low-rank latent, clamped gated feed-forward and mixtures of experts, token shift, depth average).
 This Python package is only the thin ctypes binding plus the schedulers; it never falls back to a CPU path: importing
 :mod:`host` raises if the CUDA library is missing.
 """
