@@ -90,7 +90,9 @@ __global__ void k_latent_gather(const float * __restrict__ cache, int64_t slot_s
 // CTA (head, token, 128 latent entries): qa[r] = sum_d W_uk[h * dim + d][r] q[d]; thread r walks a column of the head's block (coalesced
 // over r, eight loads in flight)
 template <typename WT>
-__global__ void __launch_bounds__(128) k_latent_absorb_q(const float * __restrict__ q, const WT * __restrict__ wuk, LatentParams p, float * __restrict__ qa) {
+__global__ void __launch_bounds__(128) k_latent_absorb_q(const float * __restrict__ q, const int32_t * __restrict__ off, const int32_t * __restrict__ pos0,
+                                                         const int32_t * __restrict__ entry_of, const WT * __restrict__ wuk, LatentParams p,
+                                                         const float * __restrict__ freq, float * __restrict__ qa) {
     extern __shared__ float qs[];   // [dim]
     const int h = blockIdx.x, t = blockIdx.y;
     const int D = p.dim, Dr = p.rot_dim, R = p.kv_rank;
@@ -113,8 +115,19 @@ __global__ void __launch_bounds__(128) k_latent_absorb_q(const float * __restric
         for (; d < D; d++) acc = fmaf(ld_f(w, (int64_t) d * R + r), qs[d], acc);
         out[r] = acc;
     }
-    if (blockIdx.z == 0)
-        for (int i = threadIdx.x; i < Dr; i += blockDim.x) out[R + i] = qr[D + i];
+    if (blockIdx.z == 0) {   // the rotated part, turned here by the token's position
+        const int e = entry_of[t], pos = pos0[e] + (t - off[e]), half = p.rot_dims / 2;
+        for (int i = threadIdx.x; i < Dr; i += blockDim.x) {
+            if (i < half) {
+                float a, b;
+                turn(qr[D + i], qr[D + i + half], pos, freq[i], p.rot_mag, a, b);
+                out[R + i] = a;
+                out[R + i + half] = b;
+            } else if (i >= 2 * half) {
+                out[R + i] = qr[D + i];
+            }
+        }
+    }
 }
 
 // one CTA per (head, token): a warp per output row of the head's block of W_uv, lanes split the latent
@@ -321,14 +334,16 @@ int launch_latent_gather(const float * cache, int64_t slot_stride, const BatchVi
         else k_latent_gather<float><<<b.n_tokens, 128, 0, st>>>(cache, slot_stride, b.slot, b.off, b.pos0, b.entry_of, p, (float *) lat, kr);
     });
 }
-int launch_latent_absorb_q(const float * q, const void * wuk, int wtype, const LatentParams & p, float * qa, int n_tokens, cudaStream_t st) {
+int launch_latent_absorb_q(const float * q, const BatchView & b, const void * wuk, int wtype, const LatentParams & p, const float * freq, float * qa,
+                           cudaStream_t st) {
+    const int n_tokens = b.n_tokens;
     if (n_tokens <= 0) return 0;
     if (!latent_ok(p)) return (int) cudaErrorInvalidValue;
     const dim3 grid((unsigned) p.heads, (unsigned) n_tokens, (unsigned) ((p.kv_rank + 127) / 128));
     const size_t smem = (size_t) p.dim * sizeof(float);
     return ck_launch([&] {
-        if (wtype == T_BF16) k_latent_absorb_q<__nv_bfloat16><<<grid, 128, smem, st>>>(q, (const __nv_bfloat16 *) wuk, p, qa);
-        else k_latent_absorb_q<float><<<grid, 128, smem, st>>>(q, (const float *) wuk, p, qa);
+        if (wtype == T_BF16) k_latent_absorb_q<__nv_bfloat16><<<grid, 128, smem, st>>>(q, b.off, b.pos0, b.entry_of, (const __nv_bfloat16 *) wuk, p, freq, qa);
+        else k_latent_absorb_q<float><<<grid, 128, smem, st>>>(q, b.off, b.pos0, b.entry_of, (const float *) wuk, p, freq, qa);
     });
 }
 int launch_latent_up_v(const float * olat, const void * wuv, int wtype, const LatentParams & p, const float * gate, int64_t ldg, void * out, int otype,

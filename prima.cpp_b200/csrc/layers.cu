@@ -1000,12 +1000,12 @@ static int mix_latent(pb200_model * m, const BatchView & b, bool prefill, const 
     CK(launch_latent_prep(ll.big, b, a, L.dq_norm.data, L.dkv_norm.data, L.rot_freq.data, ll.eps, ll.act2, ct, cache, ll.slot_floats, st));
     CAT(CAT_DENSE);
     CK(launch_dense(ct, ll.act2, a.q_rank, L.uq.data, a.q_rank, ll.big2, (int64_t) H * DQ, T, H * DQ, a.q_rank, nullptr, nullptr, 0, 1.f, st));
-    CAT(CAT_LATENT);
-    CK(launch_latent_rope_q(ll.big2, b, a, L.rot_freq.data, st));
     AttnParams ap;
     ap.heads = H; ap.scale = a.scale;
     AttnIO io;
+    CAT(CAT_LATENT);
     if (prefill) {   // keys and values of the batch, expanded from the cached latents
+        CK(launch_latent_rope_q(ll.big2, b, a, L.rot_freq.data, st));
         CK(launch_latent_gather(cache, ll.slot_floats, b, a, ll.act2, ct, ll.krb, st));
         CAT(CAT_DENSE);
         if (a.dim > 0) CK(launch_dense(ct, ll.act2, R, L.uk.data, R, ll.big3, (int64_t) H * a.dim, T, H * a.dim, R, nullptr, nullptr, 0, 1.f, st));
@@ -1019,11 +1019,11 @@ static int mix_latent(pb200_model * m, const BatchView & b, bool prefill, const 
         io.gate = gate; io.ldg = C; io.gate_mode = 2;
         CK(launch_attn_prefill_io(io, b, ap, ll.act, ct, st));
     } else if (T == b.n_entries && R <= 512) {   // one token per entry: the key up-projection folded into the query, rows split over CTAs
-        CK(launch_latent_absorb_q(ll.big2, L.uk.data, ct, a, ll.big3, T, st));
+        CK(launch_latent_absorb_q(ll.big2, b, L.uk.data, ct, a, L.rot_freq.data, ll.big3, st));
         CAT(CAT_ATTN);
         CK(launch_latent_decode(ll.big3, b, a, cache, ll.slot_floats, latent_decode_splits(a.cache_rows), ll.lat_part, L.uv.data, ct, gate, C, ll.act, ct, st));
     } else {         // the same through the shared decode kernel: one key / value head, the key is the whole row, the value its latent part
-        CK(launch_latent_absorb_q(ll.big2, L.uk.data, ct, a, ll.big3, T, st));
+        CK(launch_latent_absorb_q(ll.big2, b, L.uk.data, ct, a, L.rot_freq.data, ll.big3, st));
         CAT(CAT_ATTN);
         ap.kv_heads = 1; ap.dim = RW; ap.vdim = R; ap.cache_rows = a.cache_rows;
         io.q = ll.big3; io.ldq = (int64_t) H * RW;
@@ -1098,12 +1098,16 @@ static int ll_forward_prenorm(pb200_model * m, const BatchView & b, bool prefill
     const int64_t plane = (int64_t) ll.capT * W;
     CAT(CAT_ELEM);
     CK(launch_embed(ll.embed.data, ct, W, tokens_dev, T, ll.x, ll.hist, st));
+    bool act_ready = false;   // the kernel that closed the previous layer has left this layer's mixer input in ll.act
     for (size_t ir = 0; ir < ll.runs.size(); ir++) {
         const LRun & r = ll.runs[ir];
         LLayer & L = ll.layers[(size_t) r.layer];
         float * xn = ll.hist + (int64_t) (ir + 1) * plane;
-        CAT(CAT_NORM);
-        CK(launch_group_rmsnorm_shift(ll.x, b, L.norm1.data, G, ll.eps, L.shift.data, ll.state + r.shift_off, ll.slot_floats, ll.act, ct, W, st));
+        if (!act_ready) {
+            CAT(CAT_NORM);
+            CK(launch_group_rmsnorm_shift(ll.x, b, L.norm1.data, G, ll.eps, L.shift.data, ll.state + r.shift_off, ll.slot_floats, ll.act, ct, W, st));
+        }
+        act_ready = false;
         if (L.kind == MIX_DECAY) CK(mix_decay(m, b, r, L, ll.x, xn));
         else if (L.kind == MIX_LATENT) CK(mix_latent(m, b, prefill, r, L, ll.x, xn));
         else if (L.kind == MIX_ATTENTION) CK(mix_attention(m, b, prefill, r, L, ll.x, xn));
@@ -1114,8 +1118,17 @@ static int ll_forward_prenorm(pb200_model * m, const BatchView & b, bool prefill
             if (L.ff_kind == FF_MOE) CK(ff_moe(m, T, prefill, L, xn));
             else CK(ff_clamped(m, T, L.gateup, L.down, L.ff, L.ff_limit, xn));
         }
-        CAT(CAT_ELEM);
-        CK(launch_depth_average(ll.hist, plane, L.dwa.data, (int) ir + 2, ll.x, (int64_t) T * W, st));
+        if (b.max_n == 1 && ir + 1 < ll.runs.size()) {   // one-token entries: the depth average and the next layer's norm + shift in one kernel
+            const LRun & rn = ll.runs[ir + 1];
+            const LLayer & Ln = ll.layers[(size_t) rn.layer];
+            CAT(CAT_NORM);
+            CK(launch_depth_average_norm_shift(ll.hist, plane, L.dwa.data, (int) ir + 2, ll.x, b, Ln.norm1.data, G, ll.eps, Ln.shift.data, ll.state + rn.shift_off,
+                                               ll.slot_floats, ll.act, ct, W, st));
+            act_ready = true;
+        } else {
+            CAT(CAT_ELEM);
+            CK(launch_depth_average(ll.hist, plane, L.dwa.data, (int) ir + 2, ll.x, (int64_t) T * W, st));
+        }
         if (ll.tap_on) CK(cudaMemcpyAsync(ll.tap + (int64_t) ir * T * W, ll.x, (size_t) T * W * 4, cudaMemcpyDeviceToDevice, st));
     }
     if (nW > 0) {

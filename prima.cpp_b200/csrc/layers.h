@@ -131,6 +131,11 @@ int launch_group_rmsnorm_shift(const float * x, const BatchView & b, const float
 // out[i] = sum_{j < n} coef[j] * planes[j * plane_stride + i],  i < count
 int launch_depth_average(const float * planes, int64_t plane_stride, const float * coef, int n, float * out, int64_t count, cudaStream_t stream);
 
+// batches of one-token entries only: x = the depth average above, then launch_group_rmsnorm_shift of x (the next layer's mixer input), one kernel
+int launch_depth_average_norm_shift(const float * planes, int64_t plane_stride, const float * coef, int n, float * x, const BatchView & b, const float * w,
+                                    int groups, float eps, const float * mu, float * shift_state, int64_t slot_stride, void * y, int otype, int width,
+                                    cudaStream_t stream);
+
 // ---- linear attention with a fixed decay per head ----
 struct DecayAttnParams {
     int heads = 0, dim = 0, vdim = 0;
@@ -165,8 +170,10 @@ int launch_latent_rope_q(float * q, const BatchView & b, const LatentParams & p,
 // the batch's own cache rows: latent -> lat [T][kv_rank] (operand type), rotated key part -> kr [T][rot_dim] f32
 int launch_latent_gather(const float * cache, int64_t slot_stride, const BatchView & b, const LatentParams & p, void * lat, int otype, float * kr,
                          cudaStream_t stream);
-// decode: qa[t][h] = [ W_uk[h]^T q_unrotated[t][h]  (kv_rank) | q_rotated[t][h] (rot_dim) ]:  the score against a cache row is one dot product
-int launch_latent_absorb_q(const float * q, const void * wuk, int wtype, const LatentParams & p, float * qa, int n_tokens, cudaStream_t stream);
+// decode: qa[t][h] = [ W_uk[h]^T q_unrotated[t][h]  (kv_rank) | rotate(q[t][h][dim:], position) (rot_dim) ]: the score against a cache row is
+// one dot product.  q comes straight from the projection (not rotated yet).
+int launch_latent_absorb_q(const float * q, const BatchView & b, const void * wuk, int wtype, const LatentParams & p, const float * freq, float * qa,
+                           cudaStream_t stream);
 // decode: out[t][h][:] = (W_uv[h] olat[t][h]) * sigmoid(gate[t][h][:])   olat: [T][heads][kv_rank] (the weighted sum of latents)
 int launch_latent_up_v(const float * olat, const void * wuv, int wtype, const LatentParams & p, const float * gate, int64_t ldg, void * out, int otype,
                        int n_tokens, cudaStream_t stream);

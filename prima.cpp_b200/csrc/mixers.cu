@@ -285,13 +285,32 @@ __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const AttnIO 
         for (int k0 = lo; k0 < hi; k0 += PK) {
             const int nk = min(PK, hi - k0);
             __syncthreads();
-            for (int i = tid; i < PK * D; i += 256) {
-                const int k = i / D, d = i - k * D;
-                Kt[d * PKS + k] = k < nk ? attn_key(io, t_begin + k0 + k, kvh, d, DN) : 0.f;
+            // eight loads per thread in flight before the first store: with one CTA per SM nothing else hides a load's latency
+            for (int i0 = tid; i0 < PK * D; i0 += 256 * 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int i = i0 + 256 * u, k = i / D, d = i - k * D;
+                    v[u] = (i < PK * D && k < nk) ? attn_key(io, t_begin + k0 + k, kvh, d, DN) : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int i = i0 + 256 * u, k = i / D, d = i - k * D;
+                    if (i < PK * D) Kt[d * PKS + k] = v[u];
+                }
             }
-            for (int i = tid; i < PK * DV; i += 256) {
-                const int k = i / DV, d = i - k * DV;
-                Vs[i] = k < nk ? io.v[(int64_t) (t_begin + k0 + k) * io.ldv + kvh * DV + d] : 0.f;
+            for (int i0 = tid; i0 < PK * DV; i0 += 256 * 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int i = i0 + 256 * u, k = i / DV, d = i - k * DV;
+                    v[u] = (i < PK * DV && k < nk) ? io.v[(int64_t) (t_begin + k0 + k) * io.ldv + kvh * DV + d] : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int i = i0 + 256 * u;
+                    if (i < PK * DV) Vs[i] = v[u];
+                }
             }
             __syncthreads();
             float s[4][4];

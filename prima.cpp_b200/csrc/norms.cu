@@ -89,13 +89,82 @@ __global__ void __launch_bounds__(256) k_shift_state(const float * __restrict__ 
     for (int i = threadIdx.x; i < width; i += blockDim.x) st[i] = in[i] * inv[i / part] * w[i];
 }
 
+// sum_j coef[j] * planes[j * plane_stride + i], eight planes' loads in flight
+__device__ __forceinline__ float depth_sum(const float * __restrict__ planes, int64_t plane_stride, const float * __restrict__ coef, int n, int64_t i) {
+    float acc = 0.f;
+    int j = 0;
+    for (; j + 7 < n; j += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = planes[(int64_t) (j + u) * plane_stride + i];
+#pragma unroll
+        for (int u = 0; u < 8; u++) acc = fmaf(coef[j + u], v[u], acc);
+    }
+    for (; j < n; j++) acc = fmaf(coef[j], planes[(int64_t) j * plane_stride + i], acc);
+    return acc;
+}
 __global__ void k_depth_average(const float * __restrict__ planes, int64_t plane_stride, const float * __restrict__ coef, int n, float * __restrict__ out,
                                 int64_t count) {
     const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
-    float acc = 0.f;
-    for (int j = 0; j < n; j++) acc = fmaf(coef[j], planes[(int64_t) j * plane_stride + i], acc);
-    out[i] = acc;
+    out[i] = depth_sum(planes, plane_stride, coef, n, i);
+}
+// batches of one-token entries: the depth average that closes a layer, and the next layer's norm and token shift with its state update, on
+// one row held in shared memory
+template <typename OT>
+__global__ void __launch_bounds__(256) k_depth_average_norm_shift(const float * __restrict__ planes, int64_t plane_stride, const float * __restrict__ coef, int n,
+                                                                  float * __restrict__ x, const int32_t * __restrict__ slot, const float * __restrict__ w,
+                                                                  int groups, float eps, const float * __restrict__ mu, float * __restrict__ shift_state,
+                                                                  int64_t slot_stride, OT * __restrict__ y, int width) {
+    extern __shared__ __align__(16) float row[];   // [width]
+    __shared__ float red[33];
+    __shared__ float inv[MAX_NORM_GROUPS];
+    const int t = blockIdx.x;        // entry t brings token t
+    if ((width & 3) == 0 && (plane_stride & 3) == 0) {   // four elements per load, eight planes in flight: one CTA has to cover the row's latency alone
+        const float4 * p4 = reinterpret_cast<const float4 *>(planes + (int64_t) t * width);
+        const int64_t ps4 = plane_stride / 4;
+        for (int i = threadIdx.x; i < width / 4; i += blockDim.x) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            int j = 0;
+            for (; j + 7 < n; j += 8) {
+                float4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) v[u] = p4[(int64_t) (j + u) * ps4 + i];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const float c = coef[j + u];
+                    acc.x = fmaf(c, v[u].x, acc.x); acc.y = fmaf(c, v[u].y, acc.y); acc.z = fmaf(c, v[u].z, acc.z); acc.w = fmaf(c, v[u].w, acc.w);
+                }
+            }
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (j + u < n) v[u] = p4[(int64_t) (j + u) * ps4 + i];
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (j + u < n) {
+                    const float c = coef[j + u];
+                    acc.x = fmaf(c, v[u].x, acc.x); acc.y = fmaf(c, v[u].y, acc.y); acc.z = fmaf(c, v[u].z, acc.z); acc.w = fmaf(c, v[u].w, acc.w);
+                }
+            reinterpret_cast<float4 *>(row)[i] = acc;
+            reinterpret_cast<float4 *>(x + (int64_t) t * width)[i] = acc;
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float v = depth_sum(planes, plane_stride, coef, n, (int64_t) t * width + i);
+            row[i] = v;
+            x[(int64_t) t * width + i] = v;
+        }
+    }
+    __syncthreads();
+    group_inv_rms(row, width, groups, eps, inv, red);
+    float * st = shift_state + (int64_t) slot[t] * slot_stride;
+    const int part = width / groups;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float h = row[i] * inv[i / part] * w[i];
+        put(y, (int64_t) t * width + i, h + (st[i] - h) * mu[i]);
+        st[i] = h;
+    }
 }
 
 template <typename OT>
@@ -154,6 +223,28 @@ int launch_group_rmsnorm_shift(const float * x, const BatchView & b, const float
 int launch_depth_average(const float * planes, int64_t plane_stride, const float * coef, int n, float * out, int64_t count, cudaStream_t st) {
     if (count <= 0 || n <= 0) return 0;
     return ck_launch([&] { k_depth_average<<<(unsigned) ((count + 255) / 256), 256, 0, st>>>(planes, plane_stride, coef, n, out, count); });
+}
+int launch_depth_average_norm_shift(const float * planes, int64_t plane_stride, const float * coef, int n, float * x, const BatchView & b, const float * w,
+                                    int groups, float eps, const float * mu, float * shift_state, int64_t slot_stride, void * y, int otype, int width,
+                                    cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    if (b.max_n != 1 || b.n_tokens != b.n_entries || groups <= 0 || groups > MAX_NORM_GROUPS || width % groups != 0 || !mu || !shift_state || n <= 0)
+        return (int) cudaErrorInvalidValue;
+    const size_t smem = (size_t) width * sizeof(float);
+    if (otype == T_BF16) {
+        int rc = raise_smem(k_depth_average_norm_shift<__nv_bfloat16>, smem);
+        if (rc) return rc;
+        return ck_launch([&] {
+            k_depth_average_norm_shift<__nv_bfloat16><<<b.n_tokens, 256, smem, st>>>(planes, plane_stride, coef, n, x, b.slot, w, groups, eps, mu, shift_state,
+                                                                                     slot_stride, (__nv_bfloat16 *) y, width);
+        });
+    }
+    int rc = raise_smem(k_depth_average_norm_shift<float>, smem);
+    if (rc) return rc;
+    return ck_launch([&] {
+        k_depth_average_norm_shift<float><<<b.n_tokens, 256, smem, st>>>(planes, plane_stride, coef, n, x, b.slot, w, groups, eps, mu, shift_state, slot_stride,
+                                                                         (float *) y, width);
+    });
 }
 int launch_norm_gate(const float * y, const float * gate, int64_t ldg, int groups, const float * w, int gate_act, float eps, void * out, int otype,
                      int n_tokens, int inner, cudaStream_t st) {
