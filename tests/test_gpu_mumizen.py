@@ -350,6 +350,19 @@ def test_many_tokens_take_the_sorted_expert_path(pkg, cuda):
     m.close()
 
 
+@pytest.mark.parametrize("experts", [3, 12])
+def test_expert_products_over_wide_token_tiles(pkg, cuda, experts):
+    # 1200 (token, choice) pairs: 400 or 100 rows per expert on average, so the grouped product runs its 256- and 128-token tiles, with
+    # experts whose rows end inside a tile
+    cfg = config([lightning_layer(heads=1, dim=8, vdim=8, decay=(0.9,), mlp=moe_ff(experts=experts, top=2, ff=48, shared=None))], width=64, vocab=97, groups=2)
+    bits, W = R.random_weights(cfg, seed=21)
+    toks = tokens_for(cfg, 600, 9)
+    want, _ = R.forward(cfg, W, toks)
+    m = load(pkg, cfg, bits, "bfloat16", n_ctx=640, n_seq=2)
+    check(run_whole(m, toks), want, BF16_TOL)
+    m.close()
+
+
 def test_greedy_generation_through_the_scheduler(pkg, cuda):
     cfg = hybrid_config()
     bits, W = R.random_weights(cfg, seed=18, gain=1.5)
